@@ -1,0 +1,68 @@
+// Internal declarations shared by the .cu files of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/dlspm.h"
+
+struct dlspm_ctx {
+    int device;
+    int sm_count;
+    size_t global_mem;
+    char name[256];
+    char last_error[512];
+    int strict_fp32;  // DLSPM_OPT_STRICT_FP32
+    int spmm_kernel;  // DLSPM_OPT_SPMM_KERNEL
+    // Device scratch owned by the context, grown on demand (grouped-launch tables, staging for
+    // the host-buffer entry points).  Freed in dlspm_destroy.
+    void *scratch;
+    size_t scratch_bytes;
+    void *stage;  // staging for *_host entry points
+    size_t stage_bytes;
+    cudaStream_t stream;  // private stream of the *_host entry points
+};
+
+struct dlspm_plan {
+    dlspm_ctx *ctx;
+    int M, K, nnz;
+    int *row_order;  // device: rows in decreasing length bins
+    int sorted_rows; // 1 if every row's columns are ascending
+    int max_row_len;
+};
+
+// Records a CUDA failure in the context and returns DLSPM_ERR_CUDA.
+int dlspm_cuda_fail(dlspm_ctx *ctx, cudaError_t err, const char *what);
+
+#define DLSPM_CUDA_TRY(ctx, call)                                   \
+    do {                                                            \
+        cudaError_t err__ = (call);                                 \
+        if (err__ != cudaSuccess) return dlspm_cuda_fail((ctx), err__, #call); \
+    } while (0)
+
+// Makes the context's device current for the calling thread.
+static inline int dlspm_use(dlspm_ctx *ctx)
+{
+    if (!ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    cudaError_t err = cudaSetDevice(ctx->device);
+    if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaSetDevice");
+    return DLSPM_OK;
+}
+
+// Grows ctx->scratch to at least `bytes` (contents are not preserved).
+int dlspm_scratch_reserve(dlspm_ctx *ctx, size_t bytes);
+int dlspm_stage_reserve(dlspm_ctx *ctx, size_t bytes);
+
+static inline int dlspm_ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline long long dlspm_ceil_div64(long long a, long long b) { return (a + b - 1) / b; }
+
+// Widest vector (in floats) usable for rows of `N` floats starting at these base pointers.
+static inline int dlspm_vec_width(int N, const void *p0, const void *p1, const void *p2 = nullptr,
+                                  const void *p3 = nullptr)
+{
+    uintptr_t bits = (uintptr_t)p0 | (uintptr_t)p1 | (uintptr_t)p2 | (uintptr_t)p3;
+    if ((N % 4 == 0) && (bits % 16 == 0)) return 4;
+    if ((N % 2 == 0) && (bits % 8 == 0)) return 2;
+    return 1;
+}

@@ -1,0 +1,196 @@
+// Context, status text, options, scratch management and the fp32 peak probe.
+#include <new>
+
+#include "common.cuh"
+
+int dlspm_cuda_fail(dlspm_ctx *ctx, cudaError_t err, const char *what)
+{
+    if (ctx) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error), "%s: %s (%s)", what,
+                 cudaGetErrorString(err), cudaGetErrorName(err));
+    }
+    // Clear the sticky-free error state so that a later, unrelated call does not report it.
+    (void)cudaGetLastError();
+    return DLSPM_ERR_CUDA;
+}
+
+extern "C" const char *dlspm_strerror(int status)
+{
+    switch (status) {
+    case DLSPM_OK: return "ok";
+    case DLSPM_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case DLSPM_ERR_CUDA: return "CUDA runtime error";
+    case DLSPM_ERR_IO: return "Error opening file!";
+    case DLSPM_ERR_FORMAT: return "malformed .smtx text";
+    case DLSPM_ERR_CSR: return "CSR structure failed the sanity check";
+    case DLSPM_ERR_NOMEM: return "out of memory";
+    case DLSPM_ERR_UNSUPPORTED: return "size beyond a documented limit";
+    case DLSPM_ERR_NO_DEVICE: return "no usable CUDA device";
+    default: return "unknown status";
+    }
+}
+
+extern "C" int dlspm_create(dlspm_ctx **out, int device)
+{
+    if (!out || device < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        (void)cudaGetLastError();
+        return DLSPM_ERR_NO_DEVICE;
+    }
+    if (device >= count) return DLSPM_ERR_NO_DEVICE;
+    dlspm_ctx *ctx = new (std::nothrow) dlspm_ctx();
+    if (!ctx) return DLSPM_ERR_NOMEM;
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete ctx;
+        return DLSPM_ERR_NO_DEVICE;
+    }
+    // The kernels are built for sm_100a only; any other device cannot run them.
+    if (prop.major != 10) {
+        delete ctx;
+        return DLSPM_ERR_NO_DEVICE;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->global_mem = prop.totalGlobalMem;
+    snprintf(ctx->name, sizeof(ctx->name), "%s", prop.name);
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete ctx;
+        return DLSPM_ERR_CUDA;
+    }
+    *out = ctx;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_destroy(dlspm_ctx *ctx)
+{
+    if (!ctx) return DLSPM_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->stage) cudaFree(ctx->stage);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    (void)cudaGetLastError();
+    delete ctx;
+    return DLSPM_OK;
+}
+
+extern "C" const char *dlspm_last_error(const dlspm_ctx *ctx) { return ctx ? ctx->last_error : ""; }
+
+extern "C" int dlspm_device_info(const dlspm_ctx *ctx, char *name, size_t name_len, int *sm_count,
+                                 size_t *global_mem_bytes)
+{
+    if (!ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (name && name_len) snprintf(name, name_len, "%s", ctx->name);
+    if (sm_count) *sm_count = ctx->sm_count;
+    if (global_mem_bytes) *global_mem_bytes = ctx->global_mem;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_set_option(dlspm_ctx *ctx, int option, int value)
+{
+    if (!ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    switch (option) {
+    case DLSPM_OPT_STRICT_FP32: ctx->strict_fp32 = value ? 1 : 0; return DLSPM_OK;
+    case DLSPM_OPT_SPMM_KERNEL:
+        if (value < 0 || value > 2) return DLSPM_ERR_INVALID_ARGUMENT;
+        ctx->spmm_kernel = value;
+        return DLSPM_OK;
+    default: return DLSPM_ERR_INVALID_ARGUMENT;
+    }
+}
+
+extern "C" int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value)
+{
+    if (!ctx || !value) return DLSPM_ERR_INVALID_ARGUMENT;
+    switch (option) {
+    case DLSPM_OPT_STRICT_FP32: *value = ctx->strict_fp32; return DLSPM_OK;
+    case DLSPM_OPT_SPMM_KERNEL: *value = ctx->spmm_kernel; return DLSPM_OK;
+    default: return DLSPM_ERR_INVALID_ARGUMENT;
+    }
+}
+
+static int reserve(dlspm_ctx *ctx, void **buf, size_t *have, size_t bytes)
+{
+    if (bytes <= *have) return DLSPM_OK;
+    if (*buf) {
+        // Work queued on any stream may still read the old buffer.
+        DLSPM_CUDA_TRY(ctx, cudaDeviceSynchronize());
+        DLSPM_CUDA_TRY(ctx, cudaFree(*buf));
+        *buf = nullptr;
+        *have = 0;
+    }
+    size_t want = bytes + bytes / 4 + 256;
+    cudaError_t err = cudaMalloc(buf, want);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "cudaMalloc(scratch)");
+        *buf = nullptr;
+        return DLSPM_ERR_NOMEM;
+    }
+    *have = want;
+    return DLSPM_OK;
+}
+
+int dlspm_scratch_reserve(dlspm_ctx *ctx, size_t bytes)
+{
+    return reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes);
+}
+int dlspm_stage_reserve(dlspm_ctx *ctx, size_t bytes)
+{
+    return reserve(ctx, &ctx->stage, &ctx->stage_bytes, bytes);
+}
+
+extern "C" void dlspm_free_host(void *p) { free(p); }
+
+// ---- fp32 FMA peak --------------------------------------------------------------------------
+// Eight independent FMA chains per thread, registers only.  The result is written only if it
+// is a value it can never be, which keeps the compiler from deleting the loop.
+__global__ void __launch_bounds__(256) fma_peak_kernel(float *sink, int iters, float seed)
+{
+    float a0 = seed + threadIdx.x, a1 = a0 + 1.f, a2 = a0 + 2.f, a3 = a0 + 3.f;
+    float a4 = a0 + 4.f, a5 = a0 + 5.f, a6 = a0 + 6.f, a7 = a0 + 7.f;
+    const float m = 0.999f, c = 0.001f;
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            a0 = fmaf(a0, m, c); a1 = fmaf(a1, m, c); a2 = fmaf(a2, m, c); a3 = fmaf(a3, m, c);
+            a4 = fmaf(a4, m, c); a5 = fmaf(a5, m, c); a6 = fmaf(a6, m, c); a7 = fmaf(a7, m, c);
+        }
+    }
+    float s = a0 + a1 + a2 + a3 + a4 + a5 + a6 + a7;
+    if (s == -12345.678f) sink[0] = s;
+}
+
+extern "C" int dlspm_measure_fp32_peak(dlspm_ctx *ctx, double *tflops)
+{
+    if (!ctx || !tflops) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    rc = dlspm_scratch_reserve(ctx, 256);
+    if (rc) return rc;
+    const int iters = 4096;
+    const int blocks = ctx->sm_count * 8;
+    cudaEvent_t e0, e1;
+    DLSPM_CUDA_TRY(ctx, cudaEventCreate(&e0));
+    DLSPM_CUDA_TRY(ctx, cudaEventCreate(&e1));
+    float best_ms = 1e30f;
+    for (int rep = 0; rep < 5; rep++) {
+        cudaEventRecord(e0, ctx->stream);
+        fma_peak_kernel<<<blocks, 256, 0, ctx->stream>>>((float *)ctx->scratch, iters, 1.0f);
+        cudaEventRecord(e1, ctx->stream);
+        DLSPM_CUDA_TRY(ctx, cudaEventSynchronize(e1));
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best_ms) best_ms = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    const double flops = 2.0 * 64.0 * (double)iters * 256.0 * (double)blocks;
+    *tflops = flops / (best_ms * 1e-3) * 1e-12;
+    return DLSPM_OK;
+}

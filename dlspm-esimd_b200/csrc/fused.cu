@@ -1,0 +1,168 @@
+// Fused SDDMM -> SpMM for sm_100a: E = (pattern(A) .* (C * B^T)) * D, the sampled products never
+// leave the registers.
+//
+// One warp per row.  A pass takes 32 nonzeros: their dot products are formed exactly as in the
+// SDDMM kernel (group layout and transposing butterfly of sddmm_device.cuh), which leaves the score
+// of nonzero `lane` on that lane.  The same lane groups then gather the D rows of their own
+// nonzeros and accumulate score * D[col, :] into R float4 registers per lane; when the row is done
+// the 32/G group partial sums are added with shuffles and one group stores the row of E.
+// The reference keeps a 32-score vector per row in registers in the same way
+// (FUSED/fused-esimd_cb.cpp:130-154); it needs a zeroed E for empty rows, this kernel writes them.
+#include "common.cuh"
+#include "sddmm_device.cuh"
+
+using namespace dlspm;
+
+namespace {
+
+constexpr int kWarps = 8;
+
+template <int G, int R>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                  const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
+                  float *__restrict__ e, int M, int chunks)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const int g = lane / G, t = lane % G;
+    const float4 *c4 = reinterpret_cast<const float4 *>(c) + (size_t)row * (size_t)chunks;
+    const float4 *b4 = reinterpret_cast<const float4 *>(b);
+    const float4 *d4 = reinterpret_cast<const float4 *>(d);
+    float4 q[R];
+    load_row_chunks<G, R>(c4, chunks, t, q);
+    float4 acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        const int col = p < end ? __ldg(cols + p) : -1;
+        const float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
+#pragma unroll
+        for (int k = 0; k < G; k++) {
+            const int src = g * G + k;
+            const int cc = __shfl_sync(0xffffffffu, col, src);
+            const float s = __shfl_sync(0xffffffffu, score, src);
+            if (cc >= 0) {
+                const float4 *drow = d4 + (size_t)cc * (size_t)chunks;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int idx = r * G + t;
+                    if (idx < chunks) {
+                        const float4 v = __ldg(drow + idx);
+                        acc[r].x = fmaf(s, v.x, acc[r].x);
+                        acc[r].y = fmaf(s, v.y, acc[r].y);
+                        acc[r].z = fmaf(s, v.z, acc[r].z);
+                        acc[r].w = fmaf(s, v.w, acc[r].w);
+                    }
+                }
+            }
+        }
+    }
+    // add the partial rows of the 32/G groups
+#pragma unroll
+    for (int s = G; s < 32; s <<= 1) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            acc[r].x += __shfl_xor_sync(0xffffffffu, acc[r].x, s);
+            acc[r].y += __shfl_xor_sync(0xffffffffu, acc[r].y, s);
+            acc[r].z += __shfl_xor_sync(0xffffffffu, acc[r].z, s);
+            acc[r].w += __shfl_xor_sync(0xffffffffu, acc[r].w, s);
+        }
+    }
+    if (g == 0) {
+        float4 *e4 = reinterpret_cast<float4 *>(e) + (size_t)row * (size_t)chunks;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int idx = r * G + t;
+            if (idx < chunks) e4[idx] = acc[r];
+        }
+    }
+}
+
+// Any N and alignment.  The output row is produced in slabs of 128 columns per pass over the row's
+// nonzeros; scores are recomputed for every slab, so nothing is spilled to memory.
+__global__ void __launch_bounds__(kWarps * 32)
+fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                     const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
+                     float *__restrict__ e, int M, int N)
+{
+    constexpr int U = 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const float *crow = c + (size_t)row * (size_t)N;
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    for (int n0 = 0; n0 < N; n0 += 32 * U) {
+        float acc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) acc[u] = 0.f;
+        for (int base = start; base < end; base += 32) {
+            const int p = base + lane;
+            const int col = p < end ? __ldg(cols + p) : 0;
+            const int cnt = min(32, end - base);
+            for (int k = 0; k < cnt; k++) {
+                const int cc = __shfl_sync(0xffffffffu, col, k);
+                const float *brow = b + (size_t)cc * (size_t)N;
+                float s = 0.f;
+                for (int l = lane; l < N; l += 32) s = fmaf(__ldg(crow + l), __ldg(brow + l), s);
+#pragma unroll
+                for (int w = 16; w >= 1; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+                const float *drow = d + (size_t)cc * (size_t)N;
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int j = n0 + u * 32 + lane;
+                    if (j < N) acc[u] = fmaf(s, __ldg(drow + j), acc[u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int j = n0 + u * 32 + lane;
+            if (j < N) e[(size_t)row * (size_t)N + j] = acc[u];
+        }
+    }
+}
+
+template <int G, int R>
+void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
+                 int M, int chunks, cudaStream_t st)
+{
+    fused_rows_kernel<G, R><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks);
+}
+
+}  // namespace
+
+extern "C" int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                                          const int *row_offsets, const int *column_indices,
+                                          const float *C, const float *B, const float *D, float *E,
+                                          void *stream)
+{
+    if (!ctx || M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && !column_indices) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && N > 0 && (!C || !E)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && N > 0 && (!B || !D)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return DLSPM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = dlspm_vec_width(N, C, B, D, E);
+    int G = 0, R = 0;
+    if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
+        const int chunks = N / 4;
+        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        else launch_fast<32, 8>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+    } else {
+        fused_generic_kernel<<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N);
+    }
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}

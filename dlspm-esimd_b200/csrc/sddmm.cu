@@ -1,0 +1,128 @@
+// Sampled dense-dense matrix multiplication on a CSR pattern for sm_100a.
+//
+// One warp per row of the pattern.  The lhs row lives in registers for the whole row; rhs rows are
+// gathered with 128-bit loads; dot products are finished with a transposing butterfly (see
+// sddmm_device.cuh), and the 32 results of a pass are written with one coalesced store.  There are
+// no atomics (the reference's v4 kernel adds partial sums atomically and needs a zeroed output,
+// SDDMM/sddmm-esimd-fromfile_v4.hpp:161), so results are deterministic and every output element is
+// written exactly once.
+#include "common.cuh"
+#include "sddmm_device.cuh"
+
+using namespace dlspm;
+
+namespace {
+
+constexpr int kWarps = 8;
+
+template <int G, int R>
+__global__ void __launch_bounds__(kWarps * 32)
+sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                  const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
+                  int M, int chunks)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const int g = lane / G, t = lane % G;
+    const float4 *lhs4 = reinterpret_cast<const float4 *>(lhs) + (size_t)row * (size_t)chunks;
+    const float4 *rhs4 = reinterpret_cast<const float4 *>(rhs);
+    float4 a[R];
+    load_row_chunks<G, R>(lhs4, chunks, t, a);
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        const int col = p < end ? __ldg(cols + p) : -1;
+        const float r = sddmm_pass<G, R>(a, rhs4, chunks, col, g, t);
+        if (p < end) out[p] = r;
+    }
+}
+
+// Any N and alignment: each lane strides over the row; one full-warp reduction per nonzero.
+template <int VEC>
+__global__ void __launch_bounds__(kWarps * 32)
+sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                     const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
+                     int M, int N)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const float *arow = lhs + (size_t)row * (size_t)N;
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        const int col = p < end ? __ldg(cols + p) : 0;
+        const int cnt = min(32, end - base);
+        float mine = 0.f;
+        for (int k = 0; k < cnt; k++) {
+            const int c = __shfl_sync(0xffffffffu, col, k);
+            const float *brow = rhs + (size_t)c * (size_t)N;
+            float acc = 0.f;
+            for (int l = lane * VEC; l < N; l += 32 * VEC) {
+                if constexpr (VEC == 4) {
+                    acc = dot4(__ldg(reinterpret_cast<const float4 *>(arow + l)),
+                               __ldg(reinterpret_cast<const float4 *>(brow + l)), acc);
+                } else if constexpr (VEC == 2) {
+                    const float2 x = __ldg(reinterpret_cast<const float2 *>(arow + l));
+                    const float2 y = __ldg(reinterpret_cast<const float2 *>(brow + l));
+                    acc = fmaf(x.x, y.x, acc);
+                    acc = fmaf(x.y, y.y, acc);
+                } else {
+                    acc = fmaf(__ldg(arow + l), __ldg(brow + l), acc);
+                }
+            }
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+            if (lane == k) mine = acc;
+        }
+        if (p < end) out[p] = mine;
+    }
+}
+
+template <int G, int R>
+void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M,
+                 int chunks, cudaStream_t st)
+{
+    sddmm_rows_kernel<G, R><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks);
+}
+
+}  // namespace
+
+extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                                   const int *column_indices, const float *lhs, const float *rhs,
+                                   float *out_values, void *stream)
+{
+    if (!ctx || M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && (!column_indices || !out_values)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && N > 0 && (!lhs || !rhs)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 0 || nnz == 0) return DLSPM_OK;
+    if (N == 0) {  // empty dot products
+        DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(out_values, 0, sizeof(float) * (size_t)nnz, st));
+        return DLSPM_OK;
+    }
+    const int vec = dlspm_vec_width(N, lhs, rhs);
+    int G = 0, R = 0;
+    const int blocks = dlspm_ceil_div(M, kWarps);
+    if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
+        const int chunks = N / 4;
+        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+    } else if (vec == 4) {
+        sddmm_generic_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+    } else if (vec == 2) {
+        sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+    } else {
+        sddmm_generic_kernel<1><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+    }
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}

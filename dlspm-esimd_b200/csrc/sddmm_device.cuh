@@ -1,0 +1,91 @@
+// Device-side building blocks shared by the SDDMM and the fused SDDMM->SpMM kernels.
+//
+// Lane layout of the fast path (rows of N = 4*chunks floats, 16-byte aligned): the warp is cut
+// into 32/G groups of G lanes.  Lane t of a group owns the float4 chunks r*G + t (r = 0..R-1) of a
+// dense row, so a group reads G*16 contiguous bytes of a row per load (G >= 8: at least one full
+// 128-byte line).  One pass handles 32 nonzeros: group g takes the nonzeros g*G .. g*G+G-1 of the
+// pass and every lane keeps G partial dot products.  A transposing butterfly then leaves, on lane
+// g*G + t, the finished dot product of nonzero g*G + t: G-1 shuffles per lane for G results,
+// instead of log2(G) shuffles per result.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace dlspm {
+
+__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc)
+{
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc);
+    acc = fmaf(a.w, b.w, acc);
+    return acc;
+}
+
+// v[0..G-1] per lane -> v[0] on lane t (within its group of G lanes) = sum over the group's
+// lanes of v[t].
+template <int G>
+__device__ __forceinline__ void group_transpose_reduce(float (&v)[G], int t)
+{
+#pragma unroll
+    for (int s = G / 2; s >= 1; s >>= 1) {
+        const bool upper = (t & s) != 0;
+#pragma unroll
+        for (int k = 0; k < s; k++) {
+            const float send = upper ? v[k] : v[k + s];
+            const float keep = upper ? v[k + s] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+    }
+}
+
+// Loads the R chunks of row `row4` (a float4 pointer to the start of the row) owned by lane t.
+template <int G, int R>
+__device__ __forceinline__ void load_row_chunks(const float4 *__restrict__ row4, int chunks, int t,
+                                                float4 (&a)[R])
+{
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int idx = r * G + t;
+        a[r] = idx < chunks ? __ldg(row4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+// One pass of sampled dot products: col = this lane's column index of nonzero base+lane (or -1
+// past the end of the row).  On return part0 on lane g*G+t is dot(lhs_row, rhs[col of that lane]).
+template <int G, int R>
+__device__ __forceinline__ float sddmm_pass(const float4 (&a)[R], const float4 *__restrict__ rhs4,
+                                            int chunks, int col, int g, int t)
+{
+    float part[G];
+#pragma unroll
+    for (int k = 0; k < G; k++) {
+        const int c = __shfl_sync(0xffffffffu, col, g * G + k);
+        float acc = 0.f;
+        if (c >= 0) {
+            const float4 *brow = rhs4 + (size_t)c * (size_t)chunks;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int idx = r * G + t;
+                if (idx < chunks) acc = dot4(a[r], __ldg(brow + idx), acc);
+            }
+        }
+        part[k] = acc;
+    }
+    group_transpose_reduce<G>(part, t);
+    return part[0];
+}
+
+// Group width and chunks per lane for a row of `chunks` float4: G*R >= chunks with G >= 8.
+// Returns false when the row is too long for the register-resident path.
+__host__ __device__ inline bool sddmm_layout(int chunks, int *G, int *R)
+{
+    if (chunks <= 32) { *G = 8; }        // N <= 128
+    else if (chunks <= 64) { *G = 16; }  // N <= 256
+    else if (chunks <= 256) { *G = 32; } // N <= 1024
+    else return false;
+    const int need = (chunks + *G - 1) / *G;
+    *R = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+    return true;
+}
+
+}  // namespace dlspm

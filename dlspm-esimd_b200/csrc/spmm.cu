@@ -1,0 +1,461 @@
+// CSR SpMM for sm_100a: single-matrix launch, planned launch (rows binned by length) and the
+// grouped launch over many independent problems.
+//
+// Thread-block tile: 8 warps = 8 rows of C times one slab of 32*VEC*U columns.  Tiles are
+// numbered slab-major, so thread blocks that run at the same time work on the same columns of B
+// and share them through L2/L1.
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "spmm_device.cuh"
+
+using namespace dlspm;
+
+namespace {
+
+struct SpmmArgs {
+    const float *values;
+    const int *row_offsets;
+    const int *cols;
+    const float *B;
+    float *C;
+    const int *row_order;  // nullptr = natural order
+    int M, N;
+    int row_groups;  // ceil(M / 8)
+};
+
+template <int VEC, int U, bool STRICT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const SpmmArgs a)
+{
+    __shared__ int2 stage[kWarpsPerCta][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long tile = blockIdx.x;
+    const int slab = (int)(tile / a.row_groups);
+    const int rg = (int)(tile - (long long)slab * a.row_groups);
+    const int slot = rg * kWarpsPerCta + warp;
+    if (slot >= a.M) return;
+    const int row = a.row_order ? a.row_order[slot] : slot;
+    const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
+    spmm_warp_row_slab<VEC, U, STRICT>(a.values, a.cols, start, end, a.B,
+                                       a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * U, lane,
+                                       stage[warp]);
+}
+
+template <int VEC, int U>
+void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
+{
+    const long long tiles = (long long)a.row_groups * slabs;
+    dim3 grid((unsigned)tiles), block(kWarpsPerCta * 32);
+    if (strict) spmm_rows_kernel<VEC, U, true><<<grid, block, 0, st>>>(a);
+    else spmm_rows_kernel<VEC, U, false><<<grid, block, 0, st>>>(a);
+}
+
+template <int VEC>
+void launch_rows_vec(const SpmmArgs &a, bool strict, cudaStream_t st)
+{
+    const int U = spmm_slab_chunks(a.N, VEC);
+    const int slabs = dlspm_ceil_div(a.N, 32 * VEC * U);
+    if (U == 4) launch_rows<VEC, 4>(a, slabs, strict, st);
+    else if (U == 2) launch_rows<VEC, 2>(a, slabs, strict, st);
+    else launch_rows<VEC, 1>(a, slabs, strict, st);
+}
+
+int check_spmm_args(int M, int K, int N, int nnz, const float *values, const int *row_offsets,
+                    const int *cols, const float *B, float *C)
+{
+    if (M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && (!values || !cols || !B)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && N > 0 && !C) return DLSPM_ERR_INVALID_ARGUMENT;
+    return DLSPM_OK;
+}
+
+int spmm_launch(dlspm_ctx *ctx, int M, int N, const float *values, const int *row_offsets,
+                const int *cols, const float *B, float *C, const int *row_order, cudaStream_t st)
+{
+    if (M == 0 || N == 0) return DLSPM_OK;
+    SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta)};
+    const int vec = dlspm_vec_width(N, B, C);
+    const bool strict = ctx->strict_fp32 != 0;
+    if (vec == 4) launch_rows_vec<4>(a, strict, st);
+    else if (vec == 2) launch_rows_vec<2>(a, strict, st);
+    else launch_rows_vec<1>(a, strict, st);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_spmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                                  const int *row_offsets, const int *column_indices, const float *B,
+                                  float *C, void *stream)
+{
+    if (!ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = check_spmm_args(M, K, N, nnz, values, row_offsets, column_indices, B, C);
+    if (rc) return rc;
+    rc = dlspm_use(ctx);
+    if (rc) return rc;
+    return spmm_launch(ctx, M, N, values, row_offsets, column_indices, B, C, nullptr,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan, int N,
+                                          const float *values, const int *row_offsets,
+                                          const int *column_indices, const float *B, float *C,
+                                          void *stream)
+{
+    if (!ctx || !plan || plan->ctx != ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = check_spmm_args(plan->M, plan->K, N, plan->nnz, values, row_offsets, column_indices, B, C);
+    if (rc) return rc;
+    rc = dlspm_use(ctx);
+    if (rc) return rc;
+    return spmm_launch(ctx, plan->M, N, values, row_offsets, column_indices, B, C, plan->row_order,
+                       (cudaStream_t)stream);
+}
+
+// ---- plan: rows binned by length --------------------------------------------------------------
+namespace {
+
+constexpr int kBins = 33;  // bin b holds rows with 2^(b-1) <= length < 2^b; bin 0 = empty rows
+
+__device__ __forceinline__ int length_bin(int len) { return len <= 0 ? 0 : 32 - __clz(len); }
+
+// info[0..32] = rows per bin, info[33] = 1 while every row is sorted, info[34] = longest row
+__global__ void plan_hist_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                                 int M, int *info)
+{
+    __shared__ int hist[kBins];
+    __shared__ int s_sorted, s_max;
+    if (threadIdx.x < kBins) hist[threadIdx.x] = 0;
+    if (threadIdx.x == 0) { s_sorted = 1; s_max = 0; }
+    __syncthreads();
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
+        const int s = row_offsets[r], e = row_offsets[r + 1];
+        atomicAdd(&hist[length_bin(e - s)], 1);
+        atomicMax(&s_max, e - s);
+        bool sorted = true;
+        for (int p = s + 1; p < e; p++) sorted &= cols[p - 1] < cols[p];
+        if (!sorted) s_sorted = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x < kBins && hist[threadIdx.x]) atomicAdd(&info[threadIdx.x], hist[threadIdx.x]);
+    if (threadIdx.x == 0) {
+        if (!s_sorted) atomicAnd(&info[kBins], 0);
+        atomicMax(&info[kBins + 1], s_max);
+    }
+}
+
+// cursor[b] = first slot of bin b when bins are laid out from the longest to the shortest
+__global__ void plan_scan_kernel(const int *info, int *cursor)
+{
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int run = 0;
+        for (int b = kBins - 1; b >= 0; b--) {
+            cursor[b] = run;
+            run += info[b];
+        }
+    }
+}
+
+__global__ void plan_scatter_kernel(const int *__restrict__ row_offsets, int M, int *cursor,
+                                    int *__restrict__ row_order)
+{
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
+        const int b = length_bin(row_offsets[r + 1] - row_offsets[r]);
+        row_order[atomicAdd(&cursor[b], 1)] = r;
+    }
+}
+
+}  // namespace
+
+extern "C" int dlspm_plan_create(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets,
+                                 const int *column_indices, void *stream, dlspm_plan **out)
+{
+    if (!ctx || !out || M < 0 || K < 0 || nnz < 0 || (M > 0 && !row_offsets) ||
+        (nnz > 0 && !column_indices))
+        return DLSPM_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    dlspm_plan *plan = new (std::nothrow) dlspm_plan();
+    if (!plan) return DLSPM_ERR_NOMEM;
+    plan->ctx = ctx;
+    plan->M = M;
+    plan->K = K;
+    plan->nnz = nnz;
+    plan->row_order = nullptr;
+    plan->sorted_rows = 1;
+    plan->max_row_len = 0;
+    if (M == 0) {
+        *out = plan;
+        return DLSPM_OK;
+    }
+    int *work = nullptr;  // [0..34] info, [40..72] cursors
+    cudaError_t err = cudaMalloc(&plan->row_order, sizeof(int) * (size_t)M);
+    if (err == cudaSuccess) err = cudaMalloc(&work, sizeof(int) * 80);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "cudaMalloc(plan)");
+        if (plan->row_order) cudaFree(plan->row_order);
+        delete plan;
+        return DLSPM_ERR_NOMEM;
+    }
+    int init[80];
+    memset(init, 0, sizeof(init));
+    init[kBins] = 1;
+    int info[kBins + 2];
+    const int blocks = std::max(1, std::min(dlspm_ceil_div(M, 256), ctx->sm_count * 8));
+    err = cudaMemcpyAsync(work, init, sizeof(init), cudaMemcpyHostToDevice, st);
+    if (err == cudaSuccess) {
+        plan_hist_kernel<<<blocks, 256, 0, st>>>(row_offsets, column_indices, M, work);
+        plan_scan_kernel<<<1, 32, 0, st>>>(work, work + 40);
+        plan_scatter_kernel<<<blocks, 256, 0, st>>>(row_offsets, M, work + 40, plan->row_order);
+        err = cudaMemcpyAsync(info, work, sizeof(info), cudaMemcpyDeviceToHost, st);
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err == cudaSuccess) err = cudaGetLastError();
+    cudaFree(work);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "plan kernels");
+        cudaFree(plan->row_order);
+        delete plan;
+        return DLSPM_ERR_CUDA;
+    }
+    plan->sorted_rows = info[kBins];
+    plan->max_row_len = info[kBins + 1];
+    *out = plan;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_plan_destroy(dlspm_plan *plan)
+{
+    if (!plan) return DLSPM_OK;
+    if (plan->row_order) {
+        cudaSetDevice(plan->ctx->device);
+        cudaFree(plan->row_order);
+    }
+    delete plan;
+    return DLSPM_OK;
+}
+
+// ---- grouped launch ---------------------------------------------------------------------------
+namespace {
+
+struct BatchProblem {
+    const float *values;
+    const int *row_offsets;
+    const int *cols;
+    const float *B;
+    float *C;
+    int M, N;
+    int row_groups;
+    int vec;     // 1, 2 or 4
+    int chunks;  // U: 1, 2 or 4
+    int pad;
+};
+
+template <int VEC, bool STRICT>
+__device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, int row, int start,
+                                             int end, int lane, int2 *stage)
+{
+    float *Crow = p.C + (size_t)row * (size_t)p.N;
+    if (p.chunks == 4)
+        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 128 * VEC, lane, stage);
+    else if (p.chunks == 2)
+        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 64 * VEC, lane, stage);
+    else
+        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 32 * VEC, lane, stage);
+}
+
+// Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
+// tile of problem i (problems are stored from the most to the least work), tile_start[count] the
+// total.
+template <bool STRICT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *__restrict__ tile_start,
+                    int count, unsigned long long *counter)
+{
+    __shared__ int2 stage[kWarpsPerCta][32];
+    __shared__ unsigned long long s_tile;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long total = tile_start[count];
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(counter, 1ull);
+        __syncthreads();
+        const long long tile = (long long)s_tile;
+        __syncthreads();
+        if (tile >= total) break;
+        int lo = 0, hi = count - 1;  // last problem whose first tile is <= tile
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(tile_start + mid) <= tile) lo = mid;
+            else hi = mid - 1;
+        }
+        const BatchProblem p = problems[lo];
+        const long long t = tile - __ldg(tile_start + lo);
+        const int slab = (int)(t / p.row_groups);
+        const int row = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
+        if (row < p.M) {
+            const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+            if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+            else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+            else batched_tile<1, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+        }
+    }
+}
+
+}  // namespace
+
+struct dlspm_batch {
+    dlspm_ctx *ctx;
+    int count;        // problems with at least one tile
+    long long tiles;
+    BatchProblem *problems;  // device
+    long long *tile_start;   // device, count + 1
+    unsigned long long *counter;  // device
+};
+
+namespace {
+
+// Builds the host-side tables for a batch: problems ordered by decreasing nnz*N.
+int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProblem> &tab,
+                 std::vector<long long> &starts)
+{
+    std::vector<int> order;
+    order.reserve(count);
+    for (int i = 0; i < count; i++) {
+        const dlspm_problem &q = problems[i];
+        int rc = check_spmm_args(q.M, q.K, q.N, q.nnz, q.values, q.row_offsets, q.column_indices,
+                                 q.B, q.C);
+        if (rc) return rc;
+        if (q.M > 0 && q.N > 0) order.push_back(i);
+    }
+    std::stable_sort(order.begin(), order.end(), [&](int x, int y) {
+        return (double)problems[x].nnz * problems[x].N > (double)problems[y].nnz * problems[y].N;
+    });
+    tab.clear();
+    starts.clear();
+    long long run = 0;
+    for (int i : order) {
+        const dlspm_problem &q = problems[i];
+        BatchProblem b;
+        b.values = q.values;
+        b.row_offsets = q.row_offsets;
+        b.cols = q.column_indices;
+        b.B = q.B;
+        b.C = q.C;
+        b.M = q.M;
+        b.N = q.N;
+        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+        b.vec = dlspm_vec_width(q.N, q.B, q.C);
+        b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.pad = 0;
+        starts.push_back(run);
+        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
+        tab.push_back(b);
+    }
+    starts.push_back(run);
+    return DLSPM_OK;
+}
+
+int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long long *d_starts,
+                        unsigned long long *d_counter, int count, long long tiles, cudaStream_t st)
+{
+    if (count == 0 || tiles == 0) return DLSPM_OK;
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 8);
+    dim3 grid((unsigned)want), block(kWarpsPerCta * 32);
+    if (ctx->strict_fp32) spmm_batched_kernel<true><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
+    else spmm_batched_kernel<false><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                  dlspm_batch **out)
+{
+    if (!ctx || !out || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    std::vector<BatchProblem> tab;
+    std::vector<long long> starts;
+    rc = build_tables(count, problems, tab, starts);
+    if (rc) return rc;
+    dlspm_batch *b = new (std::nothrow) dlspm_batch();
+    if (!b) return DLSPM_ERR_NOMEM;
+    b->ctx = ctx;
+    b->count = (int)tab.size();
+    b->tiles = starts.back();
+    b->problems = nullptr;
+    b->tile_start = nullptr;
+    b->counter = nullptr;
+    const size_t tab_bytes = sizeof(BatchProblem) * std::max<size_t>(tab.size(), 1);
+    const size_t st_bytes = sizeof(long long) * starts.size();
+    cudaError_t err = cudaMalloc(&b->problems, tab_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(&b->tile_start, st_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(&b->counter, sizeof(unsigned long long));
+    if (err == cudaSuccess && !tab.empty())
+        err = cudaMemcpy(b->problems, tab.data(), sizeof(BatchProblem) * tab.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(b->tile_start, starts.data(), st_bytes, cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "batch tables");
+        dlspm_batch_destroy(b);
+        return DLSPM_ERR_CUDA;
+    }
+    *out = b;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_batch_launch(dlspm_ctx *ctx, const dlspm_batch *batch, void *stream)
+{
+    if (!ctx || !batch || batch->ctx != ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    return batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counter, batch->count,
+                               batch->tiles, (cudaStream_t)stream);
+}
+
+extern "C" int dlspm_batch_destroy(dlspm_batch *b)
+{
+    if (!b) return DLSPM_OK;
+    cudaSetDevice(b->ctx->device);
+    if (b->problems) cudaFree(b->problems);
+    if (b->tile_start) cudaFree(b->tile_start);
+    if (b->counter) cudaFree(b->counter);
+    (void)cudaGetLastError();
+    delete b;
+    return DLSPM_OK;
+}
+
+// One-shot grouped launch: tables go to the context's scratch (no allocation once it is large
+// enough); the copy is stream-ordered, so the host vectors are pinned down by a synchronize-free
+// staging through cudaMemcpyAsync from pageable memory, which returns after the source is read.
+extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                      void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    std::vector<BatchProblem> tab;
+    std::vector<long long> starts;
+    rc = build_tables(count, problems, tab, starts);
+    if (rc) return rc;
+    if (tab.empty()) return DLSPM_OK;
+    const size_t tab_bytes = sizeof(BatchProblem) * tab.size();
+    const size_t st_off = (tab_bytes + 255) & ~(size_t)255;
+    const size_t st_bytes = sizeof(long long) * starts.size();
+    const size_t cnt_off = (st_off + st_bytes + 255) & ~(size_t)255;
+    rc = dlspm_scratch_reserve(ctx, cnt_off + 256);
+    if (rc) return rc;
+    char *base = (char *)ctx->scratch;
+    cudaStream_t st = (cudaStream_t)stream;
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, tab.data(), tab_bytes, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, starts.data(), st_bytes, cudaMemcpyHostToDevice, st));
+    return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
+                               (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
+}

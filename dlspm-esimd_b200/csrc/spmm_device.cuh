@@ -1,0 +1,108 @@
+// Device-side building block of the row-gather SpMM: one warp computes one row of C for one
+// slab of 32*VEC*U consecutive columns.
+//
+// Work layout: lane l owns the columns n0 + (u*32 + l)*VEC .. +VEC-1 for u = 0..U-1, so every
+// warp-wide load of a B row is one contiguous run of 32*VEC floats (512 bytes for VEC = 4).
+// The row's (column, value) pairs are staged 32 at a time in shared memory with one coalesced
+// load per array and read back as a broadcast, which costs one shared-memory wavefront per
+// nonzero instead of two shuffles.  Each output element accumulates its products in CSR order
+// starting from 0.0f, the same order as the reference host loop
+// (SPMM/spmm-esimd-fromfile.cpp:63-83), so STRICT = true (separate multiply and add) gives its
+// bits exactly.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace dlspm {
+
+constexpr int kWarpsPerCta = 8;
+
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float *__restrict__ p, float (&v)[VEC])
+{
+    if constexpr (VEC == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else if constexpr (VEC == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2 *>(p));
+        v[0] = t.x; v[1] = t.y;
+    } else {
+        v[0] = __ldg(p);
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec(float *__restrict__ p, const float (&v)[VEC])
+{
+    if constexpr (VEC == 4) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if constexpr (VEC == 2) {
+        *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]);
+    } else {
+        p[0] = v[0];
+    }
+}
+
+template <bool STRICT>
+__device__ __forceinline__ float mad(float a, float b, float c)
+{
+    if constexpr (STRICT) return __fadd_rn(c, __fmul_rn(a, b));
+    else return fmaf(a, b, c);
+}
+
+// stage: 32 int2 slots private to this warp.
+template <int VEC, int U, bool STRICT>
+__device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
+                                                   const int *__restrict__ cols, int start, int end,
+                                                   const float *__restrict__ B, float *__restrict__ Crow,
+                                                   int N, int n0, int lane, int2 *stage)
+{
+    float acc[U][VEC];
+    int cidx[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        cidx[u] = n0 + (u * 32 + lane) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
+    }
+
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        int2 cv = make_int2(0, 0);
+        if (p < end) cv = make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p)));
+        stage[lane] = cv;
+        __syncwarp();
+        const int cnt = min(32, end - base);
+#pragma unroll 4
+        for (int j = 0; j < cnt; j++) {
+            const int2 e = stage[j];
+            const float a = __int_as_float(e.y);
+            const float *brow = B + (size_t)e.x * (size_t)N;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (cidx[u] < N) {
+                    float b[VEC];
+                    load_vec<VEC>(brow + cidx[u], b);
+#pragma unroll
+                    for (int v = 0; v < VEC; v++) acc[u][v] = mad<STRICT>(a, b[v], acc[u][v]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        if (cidx[u] < N) store_vec<VEC>(Crow + cidx[u], acc[u]);
+    }
+}
+
+// Columns covered by one warp for a given vector width and N: wide slabs for wide N so that the
+// staging of a row's indices is amortised over more B traffic.
+__host__ __device__ inline int spmm_slab_chunks(int N, int vec)
+{
+    const int per = 32 * vec;
+    if (N > 4 * per) return 4;
+    if (N > per) return 2;
+    return 1;
+}
+
+}  // namespace dlspm

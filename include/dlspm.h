@@ -1,0 +1,254 @@
+/*
+ * dlspm.h — C ABI of the B200 (sm_100a) sparse-kernel library: CSR SpMM, SDDMM and the
+ * fused SDDMM->SpMM chain in fp32.
+ *
+ * The reference project (zubair23517/dlspm-esimd) has no library boundary; its de-facto
+ * interfaces are kernel templates that take raw device pointers, host loops with the same
+ * argument order, and command-line drivers.  Every entry point below names the reference
+ * interface it replaces (file:line inside that project).
+ *
+ * Conventions
+ *   - CSR layout is the reference's: int32 row_offsets[M+1], int32 column_indices[nnz],
+ *     fp32 values[nnz]; dense operands are row-major fp32.
+ *   - Pointers are DEVICE pointers unless the function name ends in _host.
+ *   - The caller owns every buffer it passes (as in the reference, where main() allocates
+ *     and frees everything: SPMM/spmm-esimd-fromfile.cpp:172-180,294-304).
+ *   - Every function returns a dlspm_status; nothing throws across the boundary.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ *   - Differences from the reference kernels, on purpose: arrays are exact-size (no 2*VLC
+ *     padding, SPMM/spmm-esimd-fromfile2.cpp:174-176); outputs are fully written, so no
+ *     memset before a launch is needed (the reference relies on a pre-zeroed output for
+ *     empty rows, SPMM/spmmesimd2.hpp:90-91); any N >= 1 is accepted (the reference needs
+ *     N % 16 == 0, SPMM/spmm-esimd-fromfile2.cpp:230-231); addressing is 64-bit; results
+ *     are deterministic (no atomics, unlike SDDMM/sddmm-esimd-fromfile_v4.hpp:161).
+ *   - There is no CPU fallback: without a usable CUDA device dlspm_create fails.
+ */
+#ifndef DLSPM_H
+#define DLSPM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dlspm_status {
+    DLSPM_OK = 0,
+    DLSPM_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad enum            */
+    DLSPM_ERR_CUDA = 2,             /* a CUDA runtime call failed (see dlspm_last_error) */
+    DLSPM_ERR_IO = 3,               /* file could not be opened                          */
+    DLSPM_ERR_FORMAT = 4,           /* .smtx text did not parse                          */
+    DLSPM_ERR_CSR = 5,              /* CSR structure failed the sanity check             */
+    DLSPM_ERR_NOMEM = 6,            /* host or device allocation failed                  */
+    DLSPM_ERR_UNSUPPORTED = 7,      /* size beyond a documented limit                    */
+    DLSPM_ERR_NO_DEVICE = 8         /* no CUDA device / not an sm_100 device             */
+} dlspm_status;
+
+typedef struct dlspm_ctx dlspm_ctx;   /* one per device; not shared between host threads */
+typedef struct dlspm_plan dlspm_plan; /* reusable row binning of one CSR pattern         */
+typedef struct dlspm_mg dlspm_mg;     /* a set of devices driven by one host process     */
+
+/* ---- library / context ------------------------------------------------------------ */
+
+/* Replaces the reference's queue construction (SPMM/spmm-esimd-fromfile.cpp:98). */
+int dlspm_create(dlspm_ctx **ctx, int device);
+int dlspm_destroy(dlspm_ctx *ctx);
+/* Human-readable text for a status code. */
+const char *dlspm_strerror(int status);
+/* Text of the last CUDA error seen by this context ("" if none). */
+const char *dlspm_last_error(const dlspm_ctx *ctx);
+/* Device facts the drivers print (the reference prints the device name, :101-103). */
+int dlspm_device_info(const dlspm_ctx *ctx, char *name, size_t name_len, int *sm_count,
+                      size_t *global_mem_bytes);
+
+typedef enum dlspm_option {
+    /* 1: SpMM multiplies and adds with separate roundings in CSR order, which reproduces the
+     * reference CPU loop (SPMM/spmm-esimd-fromfile.cpp:63-83, built without FMA contraction)
+     * bit for bit.  0 (default): fused multiply-add. */
+    DLSPM_OPT_STRICT_FP32 = 0,
+    /* SpMM kernel choice: 0 = automatic, 1 = row-gather kernel, 2 = shared-memory tiled kernel. */
+    DLSPM_OPT_SPMM_KERNEL = 1
+} dlspm_option;
+int dlspm_set_option(dlspm_ctx *ctx, int option, int value);
+int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value);
+
+/* ---- the three kernels ------------------------------------------------------------ */
+
+/* C[M x N] = A_csr[M x K] * B[K x N].  Replaces SpmmEsimd<CHUNK>(a_values, a_row_offsets,
+ * a_column_indices, b, c, item, MSZ, KSZ, NSZ) (SPMM/spmmesimd2.hpp:63-67) together with its
+ * launch geometry (SPMM/spmm-esimd-fromfile2.cpp:188-231); same result as the host loop Spmm
+ * (SPMM/spmm-esimd-fromfile.cpp:63-83).  Empty rows produce zeros. */
+int dlspm_spmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                       const int *row_offsets, const int *column_indices, const float *B,
+                       float *C, void *stream);
+
+/* Same with a plan (row-length binning computed once per sparsity pattern). */
+int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan, int N,
+                               const float *values, const int *row_offsets,
+                               const int *column_indices, const float *B, float *C,
+                               void *stream);
+
+/* out_values[p] = dot(lhs[i, 0:N], rhs[column_indices[p], 0:N]) for every nonzero p of row i.
+ * N is the inner (dot) dimension, as NSZ is in the reference.  Replaces smallK::Launcher(
+ * row_offsets, column_indices, lhs, rhs, out, NSZ, NT, nh_threads, NSZC, queue)
+ * (SDDMM/sddmm-esimd-fromfile_v4.hpp:255-262); same result as the host loop Sddmm
+ * (SDDMM/sddmm-esimd-fromfile_v4.cpp:18-36).  Mask values are never read (treated as 1).
+ * lhs is M x N, rhs is K x N. */
+int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                        const int *column_indices, const float *lhs, const float *rhs,
+                        float *out_values, void *stream);
+
+/* E[M x N] = (pattern(A) .* (C * B^T)) * D without writing the sampled products to memory.
+ * C is M x N, B and D are K x N.  Replaces FusedEsimd(a_row_offsets, a_column_indices, c, b,
+ * d, e, item) (FUSED/fused-esimd_cb.cpp:100-105); same result as Sddmm followed by Spmm
+ * (FUSED/fused.cpp:47-89). */
+int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                               const int *row_offsets, const int *column_indices,
+                               const float *C, const float *B, const float *D, float *E,
+                               void *stream);
+
+/* ---- plans ------------------------------------------------------------------------ */
+
+/* Bins the rows of one pattern by length so that warps of one thread block get rows of similar
+ * length and long rows start first.  The reference has a single launch geometry per matrix
+ * (ComputeNT, SPMM/spmmesimd2.hpp:30-60); this is the equivalent set-up step.  row_offsets is a
+ * device pointer; the plan keeps its own device copy of the row order. */
+int dlspm_plan_create(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets,
+                      const int *column_indices, void *stream, dlspm_plan **plan);
+int dlspm_plan_destroy(dlspm_plan *plan);
+
+/* ---- grouped launch over many independent SpMMs ------------------------------------- */
+
+typedef struct dlspm_problem {
+    int M, K, N, nnz;
+    const float *values;       /* device */
+    const int *row_offsets;    /* device */
+    const int *column_indices; /* device */
+    const float *B;            /* device, K x N */
+    float *C;                  /* device, M x N */
+} dlspm_problem;
+
+/* Runs `count` independent SpMMs in one launch.  Replaces the per-matrix process launches of
+ * the batch drivers (SPMM/batch-run-spmm_fromfile:29-47).  `problems` is a HOST array; the
+ * table is copied to device scratch owned by the context. */
+int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                           void *stream);
+
+/* A prepared batch: the problem table and its tile index live on the device, so repeated
+ * launches cost no host work. */
+typedef struct dlspm_batch dlspm_batch;
+int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                       dlspm_batch **batch);
+int dlspm_batch_launch(dlspm_ctx *ctx, const dlspm_batch *batch, void *stream);
+int dlspm_batch_destroy(dlspm_batch *batch);
+
+/* ---- host-buffer entry points (copies in and out included) ----------------------------- */
+
+/* Same operations with HOST pointers: inputs are copied to the device, the kernel runs, the
+ * result is copied back, all on the context's stream; returns after the result is on the host.
+ * These are what a caller that keeps its data in host memory (as the reference drivers do
+ * before their explicit memcpy, SPMM/spmm-esimd-fromfile.cpp:172-180) binds to. */
+int dlspm_spmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                            const int *row_offsets, const int *column_indices, const float *B,
+                            float *C);
+int dlspm_sddmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                             const int *row_offsets, const int *column_indices,
+                             const float *lhs, const float *rhs, float *out_values);
+int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                                    const int *row_offsets, const int *column_indices,
+                                    const float *C, const float *B, const float *D, float *E);
+/* Batched SpMM with host pointers inside every dlspm_problem. */
+int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_problem *problems);
+
+/* ---- .smtx reader and CSR validation (host) -------------------------------------------- */
+
+/* Reads "M, K, nnz" / M+1 row offsets / nnz column indices.  Replaces the fscanf reader in
+ * every *fromfile* driver (SPMM/spmm-esimd-fromfile.cpp:105-137).  The arrays are malloc'ed
+ * here; release them with dlspm_free_host. */
+int dlspm_read_smtx_host(const char *path, int *M, int *K, int *nnz, int **row_offsets,
+                         int **column_indices);
+/* Writes the same text format (used by tests and by the drivers' --dump option). */
+int dlspm_write_smtx_host(const char *path, int M, int K, int nnz, const int *row_offsets,
+                          const int *column_indices);
+void dlspm_free_host(void *p);
+
+/* The reference's SanityCheck (SPMM/spmm-esimd-fromfile.cpp:36-61): nnz <= M*K,
+ * row_offsets[M] == nnz, monotone offsets, row length <= K, column < K; plus the checks the
+ * reference omits (row_offsets[0] == 0, column >= 0).  Returns DLSPM_ERR_CSR on failure and, if
+ * `why` is not NULL, copies a one-line reason (the reference's exception text where it has
+ * one). */
+int dlspm_sanity_check_csr_host(int M, int K, int N, int nnz, const int *row_offsets,
+                                const int *column_indices, char *why, size_t why_len);
+
+/* ---- seeded synthetic inputs (host and device) ------------------------------------------ */
+/* One counter-based generator (splitmix64 of seed, stream and element index) defines every
+ * synthetic input, so host and device produce identical bits.  These stand in for the
+ * reference's rand()-based generators (SPMM/spmm-esimd-allbenchs2.cpp:58-77). */
+
+uint64_t dlspm_rand_u64(uint64_t seed, uint64_t stream, uint64_t index);
+/* out[i] = U(-1,1) (kind 0), U[0,1) (kind 1) or N(0,1) (kind 2, Box-Muller) of element
+ * first_index + i of (seed, stream). */
+int dlspm_gen_dense_host(float *out, size_t n, uint64_t seed, uint64_t stream,
+                         uint64_t first_index, int kind);
+int dlspm_gen_dense(dlspm_ctx *ctx, float *out, size_t n, uint64_t seed, uint64_t stream,
+                    uint64_t first_index, int kind, void *stream_);
+/* Bernoulli-per-entry pattern: entry (i,j) is present iff its 24-bit uniform is below
+ * density*2^24.  Same construction as the reference sweep generator.  column_indices has room
+ * for `capacity` entries; *nnz receives the count (DLSPM_ERR_NOMEM if it does not fit). */
+int dlspm_gen_bernoulli_csr_host(int M, int K, double density, uint64_t seed, int *row_offsets,
+                                 int *column_indices, size_t capacity, int *nnz);
+/* Row lengths clip(round(Normal(mu, cov*mu)), 0, K) with mu = K*(1-sparsity); writes the
+ * prefix sum into row_offsets[M+1]. */
+int dlspm_gen_rowlen_normal_host(int M, int K, double sparsity, double cov, uint64_t seed,
+                                 int *row_offsets);
+/* For given row_offsets, fills each row with a sorted uniform sample (without replacement) of
+ * row-length columns out of K. */
+int dlspm_gen_sample_columns_host(int M, int K, const int *row_offsets, uint64_t seed,
+                                  int *column_indices);
+int dlspm_gen_sample_columns(dlspm_ctx *ctx, int M, int K, const int *row_offsets,
+                             uint64_t seed, int *column_indices, void *stream);
+/* Banded mask: row i holds every j with |i-j| <= half_band plus Bernoulli(extra_density)
+ * extras, sorted and without duplicates. */
+int dlspm_gen_band_csr_host(int M, int K, int half_band, double extra_density, uint64_t seed,
+                            int *row_offsets, int *column_indices, size_t capacity, int *nnz);
+/* Device Bernoulli pattern in two steps: counts per row -> caller prefix-sums -> fill. */
+int dlspm_gen_bernoulli_count(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
+                              int *row_counts, void *stream);
+int dlspm_gen_bernoulli_fill(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
+                             const int *row_offsets, int *column_indices, void *stream);
+
+/* ---- partitioning for several GPUs (host, no CUDA) --------------------------------------- */
+
+/* Longest-processing-time assignment of `count` weighted items to `parts` parts: items in
+ * decreasing weight (ties: lower index first) go to the least-loaded part (ties: lower part).
+ * owner[i] receives the part of item i. */
+int dlspm_partition_lpt_host(int count, const double *weights, int parts, int *owner);
+/* Row boundaries so that each of `parts` contiguous row blocks holds about nnz/parts nonzeros:
+ * bounds[parts+1], bounds[0] = 0, bounds[parts] = M. */
+int dlspm_partition_rows_by_nnz_host(int M, const int *row_offsets, int parts, int *bounds);
+
+/* ---- one process, several devices ------------------------------------------------------- */
+
+int dlspm_mg_create(dlspm_mg **mg, int ndev, const int *devices);
+int dlspm_mg_destroy(dlspm_mg *mg);
+int dlspm_mg_device_count(const dlspm_mg *mg);
+/* Batch of independent SpMMs with HOST pointers, partitioned by nnz*N across the devices, one
+ * grouped launch per device, no exchange between devices. */
+int dlspm_mg_spmm_batched_f32_host(dlspm_mg *mg, int count, const dlspm_problem *problems);
+/* One large SpMM with HOST pointers: rows are sharded by nonzero count, B is replicated, every
+ * device computes its row block of C, and the blocks are gathered into C on the host. */
+int dlspm_mg_spmm_rowshard_f32_host(dlspm_mg *mg, int M, int K, int N, int nnz,
+                                    const float *values, const int *row_offsets,
+                                    const int *column_indices, const float *B, float *C);
+
+/* ---- measurement helpers ------------------------------------------------------------------ */
+
+/* Sustained fp32 FMA rate of the device in TFLOP/s (a register-only FMA loop over all SMs); the
+ * denominator of the compute term of the roofline. */
+int dlspm_measure_fp32_peak(dlspm_ctx *ctx, double *tflops);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLSPM_H */

@@ -1,0 +1,426 @@
+/*
+ * oracle.c — CPU restatement of the reference's host loops.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is the checker for the CUDA library, never a compute path of it: only the test
+ * suite, the smoke check and the benchmark's cpu_baseline / reference arm may load it.  The
+ * product library does not link it and has no CPU fallback.
+ *
+ * Each function follows one loop of zubair23517/dlspm-esimd, cited by file:line inside that
+ * project, with the compile-time dimensions turned into arguments.  Build with
+ * -ffp-contract=off so that "a*b + c" keeps two roundings, as the reference's g++ -O2 build
+ * does on x86-64.
+ *
+ * Parity pin: oracle_spmm_f32 is compared bit for bit with the reference's SpmmEsimdCPU,
+ * oracle_sddmm with its Sddmm, oracle_spmm_f64acc with its Spmm and oracle_fused_order with
+ * its FusedEsimdCPU, all compiled unchanged from FUSED/fused.cpp (see Makefile target `ref`),
+ * and against the golden vectors made from those objects under tests/golden/.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <pthread.h>
+#include <unistd.h>
+
+/* Minimal row-parallel runner on pthreads (no OpenMP runtime is assumed on the box): worker
+ * threads pull chunks of 16 rows from a shared counter and call body(ctx, row_begin, row_end). */
+typedef void (*oracle_rows_fn)(void *ctx, int row_begin, int row_end);
+typedef struct {
+    oracle_rows_fn body;
+    void *ctx;
+    int M;
+    int next; /* next unclaimed row, advanced with an atomic add */
+} oracle_pool;
+
+static void *oracle_worker(void *arg)
+{
+    oracle_pool *p = (oracle_pool *)arg;
+    for (;;) {
+        int b = __atomic_fetch_add(&p->next, 16, __ATOMIC_RELAXED);
+        if (b >= p->M) break;
+        int e = b + 16 < p->M ? b + 16 : p->M;
+        p->body(p->ctx, b, e);
+    }
+    return NULL;
+}
+
+static void oracle_parallel_rows(oracle_rows_fn body, void *ctx, int M, int threads)
+{
+    if (threads < 1) threads = 1;
+    if (threads > 1024) threads = 1024;
+    oracle_pool pool = {body, ctx, M, 0};
+    if (threads == 1) {
+        body(ctx, 0, M);
+        return;
+    }
+    pthread_t *tid = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)threads);
+    int started = 0;
+    for (int t = 0; t < threads - 1; t++) {
+        if (pthread_create(&tid[started], NULL, oracle_worker, &pool) == 0) started++;
+    }
+    oracle_worker(&pool);
+    for (int t = 0; t < started; t++) pthread_join(tid[t], NULL);
+    free(tid);
+}
+
+/* Arguments of one call, shared by the row-range bodies below. */
+typedef struct {
+    const float *a_values;
+    const int *row_offsets;
+    const int *column_indices;
+    const float *x; /* b (SpMM), lhs (SDDMM) */
+    const float *y; /* rhs (SDDMM) */
+    float *out;
+    int N;
+} oracle_args;
+
+/* -------- SpMM, fp32 accumulator: SPMM/spmm-esimd-fromfile.cpp:63-83 ------------------- */
+static void spmm_f32_rows(void *ctx, int row_begin, int row_end)
+{
+    const oracle_args *g = (const oracle_args *)ctx;
+    const int N = g->N;
+    for (int i = row_begin; i < row_end; ++i) {
+        for (int j = 0; j < N; ++j) {
+            float accum = 0.0f;
+            for (int l = g->row_offsets[i]; l < g->row_offsets[i + 1]; l++) {
+                float a_val = g->a_values[l];
+                int a_col = g->column_indices[l];
+                accum += a_val * g->x[(size_t)a_col * N + j];
+            }
+            g->out[(size_t)i * N + j] = accum;
+        }
+    }
+}
+
+void oracle_spmm_f32(const float *a_values, const int *a_row_offsets,
+                     const int *a_column_indices, const float *b, float *c, int M, int N)
+{
+    oracle_args g = {a_values, a_row_offsets, a_column_indices, b, NULL, c, N};
+    spmm_f32_rows(&g, 0, M);
+}
+
+/* Same loop with the rows spread over `threads` host threads (the all-cores CPU baseline).
+ * The per-element order is unchanged, so the result is bit-identical to oracle_spmm_f32. */
+void oracle_spmm_f32_mt(const float *a_values, const int *a_row_offsets,
+                        const int *a_column_indices, const float *b, float *c, int M, int N,
+                        int threads)
+{
+    oracle_args g = {a_values, a_row_offsets, a_column_indices, b, NULL, c, N};
+    oracle_parallel_rows(spmm_f32_rows, &g, M, threads);
+}
+
+/* Row-major-friendly order of the same arithmetic (loop over nonzeros outside, columns
+ * inside): every output element still sums its products in CSR order starting from 0.0f, so
+ * the bits equal oracle_spmm_f32; it is only faster.  This is the order of the reference's
+ * SpmmEsimdCPU (FUSED/fused.cpp:218-303). */
+static void spmm_f32_rowmajor_rows(void *ctx, int row_begin, int row_end)
+{
+    const oracle_args *g = (const oracle_args *)ctx;
+    const int N = g->N;
+    for (int i = row_begin; i < row_end; ++i) {
+        float *crow = g->out + (size_t)i * N;
+        for (int j = 0; j < N; ++j) crow[j] = 0.0f;
+        for (int l = g->row_offsets[i]; l < g->row_offsets[i + 1]; l++) {
+            const float av = g->a_values[l];
+            const float *brow = g->x + (size_t)g->column_indices[l] * N;
+            for (int j = 0; j < N; ++j) crow[j] = crow[j] + av * brow[j];
+        }
+    }
+}
+
+void oracle_spmm_f32_rowmajor_mt(const float *a_values, const int *a_row_offsets,
+                                 const int *a_column_indices, const float *b, float *c, int M,
+                                 int N, int threads)
+{
+    oracle_args g = {a_values, a_row_offsets, a_column_indices, b, NULL, c, N};
+    oracle_parallel_rows(spmm_f32_rowmajor_rows, &g, M, threads);
+}
+
+/* -------- SpMM, double accumulator: FUSED/fused.cpp:67-89 ------------------------------- */
+static void spmm_f64acc_rows(void *ctx, int row_begin, int row_end)
+{
+    const oracle_args *g = (const oracle_args *)ctx;
+    const int N = g->N;
+    for (int i = row_begin; i < row_end; ++i) {
+        for (int j = 0; j < N; ++j) {
+            double accum = 0.0;
+            for (int l = g->row_offsets[i]; l < g->row_offsets[i + 1]; ++l) {
+                float a_val = g->a_values[l];
+                int a_col = g->column_indices[l];
+                accum += (double)a_val * (double)g->x[(size_t)a_col * N + j];
+            }
+            g->out[(size_t)i * N + j] = (float)accum;
+        }
+    }
+}
+
+void oracle_spmm_f64acc(const float *a_values, const int *a_row_offsets,
+                        const int *a_column_indices, const float *d, float *e, int M, int N)
+{
+    oracle_args g = {a_values, a_row_offsets, a_column_indices, d, NULL, e, N};
+    spmm_f64acc_rows(&g, 0, M);
+}
+
+/* -------- SDDMM, double accumulator: SDDMM/sddmm-esimd-fromfile_v4.cpp:18-36 -------------- */
+static void sddmm_rows(void *ctx, int row_begin, int row_end)
+{
+    const oracle_args *g = (const oracle_args *)ctx;
+    const int N = g->N;
+    for (int i = row_begin; i < row_end; ++i) {
+        for (int j = g->row_offsets[i]; j < g->row_offsets[i + 1]; ++j) {
+            int idx_n = g->column_indices[j];
+            double accumulator = 0.0;
+            for (int l = 0; l < N; ++l) {
+                accumulator += (double)g->x[(size_t)i * N + l] * (double)g->y[(size_t)idx_n * N + l];
+            }
+            g->out[j] = (float)accumulator;
+        }
+    }
+}
+
+void oracle_sddmm(const int *row_offsets, const int *column_indices, const float *lhs,
+                  const float *rhs, float *out, int M, int N)
+{
+    oracle_args g = {NULL, row_offsets, column_indices, lhs, rhs, out, N};
+    sddmm_rows(&g, 0, M);
+}
+
+void oracle_sddmm_mt(const int *row_offsets, const int *column_indices, const float *lhs,
+                     const float *rhs, float *out, int M, int N, int threads)
+{
+    oracle_args g = {NULL, row_offsets, column_indices, lhs, rhs, out, N};
+    oracle_parallel_rows(sddmm_rows, &g, M, threads);
+}
+
+/* -------- fused oracle = Sddmm then Spmm (double): FUSED/fused.cpp:47-89, used :396-401 ---- */
+/* a_values is caller-provided scratch of nnz floats and receives the SDDMM result. */
+void oracle_fused(const int *row_offsets, const int *column_indices, const float *c,
+                  const float *b, const float *d, float *e, float *a_values, int M, int N)
+{
+    oracle_sddmm(row_offsets, column_indices, c, b, a_values, M, N);
+    oracle_spmm_f64acc(a_values, row_offsets, column_indices, d, e, M, N);
+}
+
+void oracle_fused_mt(const int *row_offsets, const int *column_indices, const float *c,
+                     const float *b, const float *d, float *e, float *a_values, int M, int N,
+                     int threads)
+{
+    oracle_sddmm_mt(row_offsets, column_indices, c, b, a_values, M, N, threads);
+    oracle_args g = {a_values, row_offsets, column_indices, d, NULL, e, N};
+    oracle_parallel_rows(spmm_f64acc_rows, &g, M, threads);
+}
+
+/* -------- the fp32 emulation of the fused kernel's order: FUSED/fused.cpp:93-216 ------------
+ * Per row: products c[i,m]*b[col,m] rounded to fp32, summed left to right into element 0,
+ * then e_row += score * d_row in CSR order.  The 32-wide chunking of the original does not
+ * change any per-element order, so it is dropped here. */
+void oracle_fused_order(const int *row_offsets, const int *column_indices, const float *c,
+                        const float *b, const float *d, float *e, int M, int N)
+{
+    float *e_row = (float *)malloc(sizeof(float) * (size_t)(N > 0 ? N : 1));
+    for (int i = 0; i < M; i++) {
+        for (int m = 0; m < N; m++) e_row[m] = 0.0f;
+        for (int p = row_offsets[i]; p < row_offsets[i + 1]; p++) {
+            const int col = column_indices[p];
+            float acc0 = c[(size_t)i * N] * b[(size_t)col * N];
+            for (int m = 1; m < N; m++) {
+                float prod = c[(size_t)i * N + m] * b[(size_t)col * N + m];
+                acc0 += prod;
+            }
+            for (int m = 0; m < N; m++) e_row[m] = e_row[m] + acc0 * d[(size_t)col * N + m];
+        }
+        for (int m = 0; m < N; m++) e[(size_t)i * N + m] = e_row[m];
+    }
+    free(e_row);
+}
+
+/* -------- magnitude scales for the tolerance test -------------------------------------------
+ * The reference prints max |diff| and max |diff|/max(|cpu|,|gpu|) without a threshold
+ * (SPMM/spmm-esimd-allbenchs2.cpp:205-233) and feeds non-negative inputs.  With signed inputs
+ * an output can cancel to ~0, so the pass criterion used by the tests is
+ * |out - ref| <= tol * max(|ref|, scale), scale = sum of |products| of that output. */
+void oracle_spmm_scale(const float *a_values, const int *a_row_offsets,
+                       const int *a_column_indices, const float *b, float *scale, int M, int N)
+{
+    for (int i = 0; i < M; ++i) {
+        for (int j = 0; j < N; ++j) {
+            double accum = 0.0;
+            for (int l = a_row_offsets[i]; l < a_row_offsets[i + 1]; ++l) {
+                accum += fabs((double)a_values[l]) * fabs((double)b[(size_t)a_column_indices[l] * N + j]);
+            }
+            scale[(size_t)i * N + j] = (float)accum;
+        }
+    }
+}
+
+void oracle_sddmm_scale(const int *row_offsets, const int *column_indices, const float *lhs,
+                        const float *rhs, float *scale, int M, int N)
+{
+    for (int i = 0; i < M; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            int idx_n = column_indices[j];
+            double accumulator = 0.0;
+            for (int l = 0; l < N; ++l) {
+                accumulator += fabs((double)lhs[(size_t)i * N + l]) * fabs((double)rhs[(size_t)idx_n * N + l]);
+            }
+            scale[j] = (float)accumulator;
+        }
+    }
+}
+
+/* scale of the fused output: sum_p scale_sddmm[p] * |d[col_p, j]| */
+void oracle_fused_scale(const int *row_offsets, const int *column_indices, const float *c,
+                        const float *b, const float *d, float *scale, float *sddmm_scale, int M,
+                        int N)
+{
+    oracle_sddmm_scale(row_offsets, column_indices, c, b, sddmm_scale, M, N);
+    for (int i = 0; i < M; ++i) {
+        for (int j = 0; j < N; ++j) {
+            double accum = 0.0;
+            for (int l = row_offsets[i]; l < row_offsets[i + 1]; ++l) {
+                accum += (double)sddmm_scale[l] * fabs((double)d[(size_t)column_indices[l] * N + j]);
+            }
+            scale[(size_t)i * N + j] = (float)accum;
+        }
+    }
+}
+
+/* -------- SanityCheck: SPMM/spmm-esimd-fromfile.cpp:36-61 ------------------------------------
+ * Returns 0 when the structure passes, otherwise the 1-based number of the failing check in
+ * the order the reference tests them; `why` gets the reference's exception text. */
+int oracle_sanity_check(int M, int K, int N, int nnz, const int *a_row_offsets,
+                        const int *a_column_indices, char *why, size_t why_len)
+{
+    (void)N;
+    const char *msg = NULL;
+    int code = 0;
+    if ((long long)nnz > (long long)M * (long long)K) {
+        msg = "nnz is larger than matrix.";
+        code = 1;
+    } else if (a_row_offsets[M] != nnz) {
+        msg = "a_row_offsets[MSZ] != nnz.";
+        code = 2;
+    }
+    for (int i = 0; i < M && !code; i++) {
+        if (a_row_offsets[i + 1] < a_row_offsets[i]) {
+            msg = "a_row_offsets[i+1] < a_row_offsets[i]";
+            code = 3;
+        } else if (a_row_offsets[i + 1] - a_row_offsets[i] > K) {
+            msg = "a_row_offsets[i + 1] - a_row_offsets[i] > KSZ";
+            code = 4;
+        }
+    }
+    for (int i = 0; i < nnz && !code; i++) {
+        if (a_column_indices[i] >= K) {
+            msg = "a_column_indices[i] >= KSZ";
+            code = 5;
+        }
+    }
+    if (why && why_len) {
+        snprintf(why, why_len, "%s", msg ? msg : "");
+    }
+    return code;
+}
+
+/* -------- .smtx reader: SPMM/spmm-esimd-fromfile.cpp:105-137 ------------------------------------
+ * fscanf("%d,%d,%d") header, then M+1 offsets, then nnz indices.  Returns 0 on success, 1 if
+ * the file cannot be opened, 2..4 for the three parse failures the reference throws on. */
+int oracle_read_smtx(const char *path, int *M, int *K, int *nnz, int **row_offsets,
+                     int **column_indices)
+{
+    FILE *fp = fopen(path, "r");
+    if (fp == NULL) return 1;
+    if (fscanf(fp, "%d,%d,%d", M, K, nnz) != 3) {
+        fclose(fp);
+        return 2;
+    }
+    int *ro = (int *)malloc(((size_t)*M + 1) * sizeof(int));
+    int *ci = (int *)malloc(((size_t)(*nnz > 0 ? *nnz : 1)) * sizeof(int));
+    for (int i = 0; i < *M + 1; i++) {
+        if (fscanf(fp, "%d", &ro[i]) != 1) {
+            fclose(fp);
+            free(ro);
+            free(ci);
+            return 3;
+        }
+    }
+    for (int i = 0; i < *nnz; i++) {
+        if (fscanf(fp, "%d", &ci[i]) != 1) {
+            fclose(fp);
+            free(ro);
+            free(ci);
+            return 4;
+        }
+    }
+    fclose(fp);
+    *row_offsets = ro;
+    *column_indices = ci;
+    return 0;
+}
+
+void oracle_free(void *p) { free(p); }
+
+/* -------- report helpers: FUSED/fused.cpp:305-335, SPMM/spmm-esimd-fromfile.cpp:257-284 ------ */
+double oracle_checksum_rms(const float *x, long long n)
+{
+    double sum = 0.0;
+    for (long long i = 0; i < n; i++) sum += x[i] * x[i];
+    return sqrt(sum / (double)n);
+}
+
+/* max |gold-x|, its index, and max |d|/max(|gold|,|x|) (0/0 counted as 0). */
+void oracle_validate(const float *x_gold, const float *x, long long n, double *max_diff,
+                     long long *maxi, double *max_rel_diff)
+{
+    double md = 0.0, mr = 0.0;
+    long long mi = 0;
+    for (long long i = 0; i < n; i++) {
+        double diff = fabs((double)x_gold[i] - (double)x[i]);
+        double den = fmax(fabs((double)x_gold[i]), fabs((double)x[i]));
+        if (den > 0.0 && diff / den > mr) mr = diff / den;
+        if (diff > md) {
+            md = diff;
+            mi = i;
+        }
+    }
+    *max_diff = md;
+    *maxi = mi;
+    *max_rel_diff = mr;
+}
+
+/* Number of elements violating |out-ref| <= tol*max(|ref|,scale); worst ratio in *worst. */
+long long oracle_count_violations(const float *ref, const float *out, const float *scale,
+                                  long long n, double tol, double *worst)
+{
+    long long bad = 0;
+    double w = 0.0;
+    for (long long i = 0; i < n; i++) {
+        double diff = fabs((double)ref[i] - (double)out[i]);
+        double den = fmax(fabs((double)ref[i]), (double)scale[i]);
+        if (!(diff == diff)) { /* NaN */
+            bad++;
+            w = INFINITY;
+            continue;
+        }
+        if (den == 0.0) {
+            if (diff != 0.0) {
+                bad++;
+                w = INFINITY;
+            }
+            continue;
+        }
+        double r = diff / den;
+        if (r > w) w = r;
+        if (r > tol) bad++;
+    }
+    if (worst) *worst = w;
+    return bad;
+}
+
+int oracle_max_threads(void)
+{
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    return n > 0 ? (int)n : 1;
+}
