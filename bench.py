@@ -1,0 +1,599 @@
+"""Benchmark of the B200 sparse-kernel library on the reference's headline workload.
+
+    python bench.py --gpus N --steps K --warmup W              # this library (CUDA kernels)
+    python bench.py --impl reference --gpus N --steps K ...    # the reference's CPU loop, host cores
+    torchrun --nproc-per-node N bench.py --gpus N ...          # one rank per GPU
+
+Workload (`config.workload`): the batch of 8192 independent CSR SpMMs drawn from the shape /
+sparsity / width grid of the sweep configuration (shapes 64x64 .. 1024x4096, sparsity 0.5 .. 0.98,
+row lengths Normal with CoV 0.4, N in {256, 1024, 3136}), all matrices generated on the device from
+a seed.  A step is one pass over the whole batch: one grouped launch per GPU.  With N GPUs the
+problems are dealt out by nnz*N (longest-processing-time), so total work is fixed ("strong").
+The metric is GFLOP/s = sum(2*nnz*N) / time.
+
+One JSON line is printed by rank 0.  Besides the contract keys it carries `roofline` (algorithmic
+bytes of rank 0's launch over its event-timed duration, against the measured HBM copy bandwidth),
+`e2e` (the same metric through the host-buffer C-ABI call, copies included, on a stated sample of
+the batch), `cpu_baseline` (the CPU oracle on the host cores, N=1 only) and `extras` (the other
+configurations: single SpMM, SDDMM, fused, the 90 % sparsity sweep, the row-sharded large SpMM).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+SHAPES = [(64, 64), (256, 256), (512, 2048), (2048, 512), (1024, 4096)]
+SPARSITIES = [0.5, 0.7, 0.8, 0.9, 0.95, 0.98]
+WIDTHS = [256, 1024, 3136]
+COV = 0.4
+STREAM_PICK = 50
+FALLBACK_HBM_GBS = 6650.0
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def align(n: int, a: int = 64) -> int:
+    return (n + a - 1) // a * a
+
+
+# ---- workload description ------------------------------------------------------------------------------
+
+def batch_descriptors(pkg, count: int, seed: int):
+    """(M, K, N, sparsity, problem_seed, row_offsets) for every problem of the batch."""
+    out = []
+    for k in range(count):
+        h = pkg.rand_u64(seed, STREAM_PICK, k)
+        M, K = SHAPES[h % 5]
+        sp = SPARSITIES[(h >> 8) % 6]
+        N = WIDTHS[(h >> 16) % 3]
+        pseed = seed * (1 << 20) + k
+        ro = pkg.gen_rowlen_normal_host(M, K, sp, COV, pseed)
+        out.append((M, K, N, sp, pseed, ro))
+    return out
+
+
+def spmm_bytes(M, K, N, nnz):
+    """Algorithmic bytes of one SpMM: A once, B once, C written once."""
+    return 4 * (M + 1) + 8 * nnz + 4 * K * N + 4 * M * N
+
+
+class DeviceBatch:
+    """The problems of one rank, generated in two device pools (int32 and fp32)."""
+
+    def __init__(self, pkg, ctx, dev, descs, mine):
+        import torch
+
+        self.pkg, self.ctx, self.dev = pkg, ctx, dev
+        self.items = [descs[i] for i in mine]
+        n_ro = n_int = n_flt = 0
+        self.layout = []
+        for (M, K, N, sp, pseed, ro) in self.items:
+            nnz = int(ro[-1])
+            o_ro = n_ro
+            n_ro += align(M + 1)
+            o_ci = n_int
+            n_int += align(nnz)
+            o_v = n_flt
+            n_flt += align(nnz)
+            o_B = n_flt
+            n_flt += align(K * N)
+            o_C = n_flt
+            n_flt += align(M * N)
+            self.layout.append((o_ro, o_ci, o_v, o_B, o_C, nnz))
+        self.ipool = torch.empty(max(n_int, 1), dtype=torch.int32, device=dev)
+        self.fpool = torch.empty(max(n_flt, 1), dtype=torch.float32, device=dev)
+        self.bytes_device = 4 * (n_ro + n_int + n_flt)
+        # row offsets: one host array in pool layout, one copy
+        host_ro = np.zeros(max(n_ro, 1), dtype=np.int32)
+        for (M, K, N, sp, pseed, ro), (o_ro, *_rest) in zip(self.items, self.layout):
+            host_ro[o_ro:o_ro + M + 1] = ro
+        self.rpool = torch.from_numpy(host_ro).to(dev)
+        self.flops = 0.0
+        self.alg_bytes = 0.0
+        self.problems = pkg.ProblemArray(len(self.items))
+        rb, ib, fb = self.rpool.data_ptr(), self.ipool.data_ptr(), self.fpool.data_ptr()
+        for i, ((M, K, N, sp, pseed, ro), (o_ro, o_ci, o_v, o_B, o_C, nnz)) in enumerate(zip(self.items, self.layout)):
+            ro_t = self.rpool[o_ro:o_ro + M + 1]
+            ctx.gen_sample_columns(M, K, ro_t, pseed, self.ipool[o_ci:o_ci + max(nnz, 1)])
+            if nnz:
+                ctx.gen_dense(self.fpool[o_v:o_v + nnz], pseed, 2)
+            ctx.gen_dense(self.fpool[o_B:o_B + K * N], pseed, 10)
+            self.problems.set_raw(i, M, K, N, nnz, fb + 4 * o_v if nnz else None, rb + 4 * o_ro,
+                                  ib + 4 * o_ci if nnz else None, fb + 4 * o_B, fb + 4 * o_C)
+            self.flops += 2.0 * nnz * N
+            self.alg_bytes += spmm_bytes(M, K, N, nnz)
+        torch.cuda.synchronize()
+        self.batch = ctx.batch_create(self.problems)
+
+    def host_sample(self, max_bytes: int, max_problems: int):
+        """Pinned host copies of the first problems of this rank (inputs) plus pinned outputs."""
+        import torch
+
+        arr_items = []
+        total = 0
+        for (M, K, N, sp, pseed, ro), (o_ro, o_ci, o_v, o_B, o_C, nnz) in zip(self.items, self.layout):
+            b = spmm_bytes(M, K, N, nnz)
+            if arr_items and (total + b > max_bytes or len(arr_items) >= max_problems):
+                break
+            total += b
+            h_ro = self.rpool[o_ro:o_ro + M + 1].cpu().pin_memory()
+            h_ci = self.ipool[o_ci:o_ci + nnz].cpu().pin_memory()
+            h_v = self.fpool[o_v:o_v + nnz].cpu().pin_memory()
+            h_B = self.fpool[o_B:o_B + K * N].cpu().pin_memory()
+            h_C = torch.empty(M * N, dtype=torch.float32).pin_memory()
+            arr_items.append((M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C))
+        arr = self.pkg.ProblemArray(len(arr_items))
+        flops = h2d = d2h = 0.0
+        for i, (M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C) in enumerate(arr_items):
+            arr.set(i, M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C, host=True)
+            flops += 2.0 * nnz * N
+            h2d += 4 * (M + 1) + 8 * nnz + 4 * K * N
+            d2h += 4 * M * N
+        return arr, arr_items, flops, h2d, d2h
+
+
+# ---- clocks ------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, dev_index: int):
+        import torch
+
+        self.proc = None
+        self.path = f"/tmp/dlspm_clocks_{os.getpid()}.csv"
+        try:
+            uuid = str(torch.cuda.get_device_properties(dev_index).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", ident, f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception as e:  # nvidia-smi missing: report empty clocks
+            log("clock sampler unavailable:", e)
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---- CPU baseline (the oracle: the reference's host loop, rows spread over the host threads) -----------------
+
+def cpu_sample(pkg, descs, budget_flops: float):
+    """Problems for the CPU arm, regenerated on the host (same bits as the device generators)."""
+    order = sorted(range(len(descs)), key=lambda i: float(descs[i][5][-1]) * descs[i][2])
+    # walk from the median-cost problem outwards so that the sample is neither all tiny nor all huge
+    mid = len(order) // 2
+    walk = [order[mid]]
+    for step in range(1, len(order)):
+        for pos in (mid - step, mid + step):
+            if 0 <= pos < len(order):
+                walk.append(order[pos])
+    picked, flops = [], 0.0
+    for i in walk:
+        M, K, N, sp, pseed, ro = descs[i]
+        f = 2.0 * float(ro[-1]) * N
+        if picked and flops + f > budget_flops:
+            break
+        picked.append(i)
+        flops += f
+    data = []
+    for i in picked:
+        M, K, N, sp, pseed, ro = descs[i]
+        ci = pkg.gen_sample_columns_host(M, K, ro, pseed)
+        vals = pkg.gen_dense_host(int(ci.size), pseed, 2)
+        B = pkg.gen_dense_host(K * N, pseed, 10).reshape(K, N)
+        data.append((M, K, N, ro, ci, vals, B))
+    return data, flops
+
+
+def time_cpu(oracle, data, threads: int) -> float:
+    t0 = time.perf_counter()
+    for (M, K, N, ro, ci, vals, B) in data:
+        oracle.spmm(vals, ro, ci, B, M, N, threads=max(threads, 2))
+    return time.perf_counter() - t0
+
+
+def cpu_rate_probe(pkg, oracle, threads):
+    """GFLOP/s of the CPU loop on one mid-sized problem (sizes the bounded sample)."""
+    M, K, N = 256, 256, 256
+    ro = pkg.gen_rowlen_normal_host(M, K, 0.8, COV, 99)
+    ci = pkg.gen_sample_columns_host(M, K, ro, 99)
+    vals = pkg.gen_dense_host(int(ci.size), 99, 2)
+    B = pkg.gen_dense_host(K * N, 99, 10).reshape(K, N)
+    t = time_cpu(oracle, [(M, K, N, ro, ci, vals, B)], threads)
+    return 2.0 * ci.size * N / t * 1e-9
+
+
+def run_reference_arm(args, rank, world):
+    """Times the reference's own CPU implementation of the path (the pinned oracle) on host cores."""
+    if rank != 0:
+        return
+    pkg = entry.load_package()
+    oracle = entry.load_oracle()
+    threads = oracle.max_threads()
+    descs = batch_descriptors(pkg, args.problems, args.seed)
+    rate = cpu_rate_probe(pkg, oracle, threads)
+    steps_total = max(1, args.steps + args.warmup)
+    budget_s = min(20.0, 150.0 / steps_total)
+    data, flops = cpu_sample(pkg, descs, rate * 1e9 * budget_s)
+    for _ in range(args.warmup):
+        time_cpu(oracle, data, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        time_cpu(oracle, data, threads)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    gflops = flops / dt * 1e-9
+    sample = f"{len(data)} problems of the batch around the median cost ({flops / 1e9:.2f} GFLOP per step)"
+    line = {
+        "impl": "reference", "metric": "spmm_batch_gflops", "value": gflops, "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, world),
+        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": f"batch of {args.problems} independent CSR SpMMs from the sweep grid "
+                        "(5 shapes x 6 sparsities x N in {256,1024,3136}, row-length CoV 0.4), fp32",
+            "problems": args.problems, "seed": args.seed, "partition": f"lpt by nnz*N over {world} gpu(s)",
+            "l2": "inputs larger than L2 (no flush needed)"}
+
+
+# ---- extras: the other configurations ---------------------------------------------------------------------------
+
+def time_kernel(fn, reps, flush=None):
+    """Per-launch device times in ms (CUDA events on the current stream)."""
+    import torch
+
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.fill_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return times
+
+
+def summarize(times_warm, times_cold, flops, nbytes, hbm_gbs, fp32_tflops):
+    warm, cold = min(times_warm), statistics.median(times_cold)
+    t_roof_ms = max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3
+    return {"us_warm_min": warm * 1e3, "us_cold_median": cold * 1e3,
+            "gflops_warm": flops / warm * 1e-6, "gflops_cold": flops / cold * 1e-6,
+            "hbm_gbs_cold": nbytes / cold * 1e-6, "hbm_frac_cold": nbytes / cold * 1e-6 / hbm_gbs,
+            "roof_frac_cold": t_roof_ms / cold, "roof_frac_warm": t_roof_ms / warm,
+            "binds": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (fp32_tflops * 1e12) else "fp32"}
+
+
+def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
+    import torch
+
+    out = {}
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=dev)  # 256 MiB > L2
+
+    def up(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+    # single SpMM 512 x 512, density 0.1, N = 128
+    M, K, N = 512, 512, 128
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.1, 1)
+    nnz = int(ci.size)
+    d = [up(pkg.gen_dense_host(nnz, 1, 2)), up(ro), up(ci), up(pkg.gen_dense_host(K * N, 1, 10)), torch.empty(M * N, device=dev)]
+    fn = lambda: ctx.spmm(M, K, N, nnz, *d)
+    fn(); fn()
+    out["spmm_512x512_d0.1_n128"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+                                               spmm_bytes(M, K, N, nnz), hbm_gbs, fp32_tflops)
+
+    # SDDMM 2048 x 512 mask at density 0.2, inner dimension 128
+    M, K, N = 2048, 512, 128
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.2, 2)
+    nnz = int(ci.size)
+    s = [up(ro), up(ci), up(pkg.gen_dense_host(M * N, 2, 11, kind=2)), up(pkg.gen_dense_host(K * N, 2, 12, kind=2)),
+         torch.empty(nnz, device=dev)]
+    fn = lambda: ctx.sddmm(M, K, N, nnz, *s)
+    fn(); fn()
+    out["sddmm_2048x512_d0.2_n128"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+                                                 4 * (M + 1) + 8 * nnz + 4 * M * N + 4 * K * N, hbm_gbs, fp32_tflops)
+
+    # fused SDDMM -> SpMM, band(64) + 5 % mask 4096 x 4096, d = 64
+    M = K = 4096
+    N = 64
+    ro, ci = pkg.gen_band_csr_host(M, K, 32, 0.05, 4)
+    nnz = int(ci.size)
+    f = [up(ro), up(ci), up(pkg.gen_dense_host(M * N, 4, 11, kind=2)), up(pkg.gen_dense_host(K * N, 4, 12, kind=2)),
+         up(pkg.gen_dense_host(K * N, 4, 13, kind=2)), torch.empty(M * N, device=dev)]
+    fn = lambda: ctx.fused(M, K, N, nnz, *f)
+    fn(); fn()
+    out["fused_band4096_d64"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 4.0 * nnz * N,
+                                          4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N, hbm_gbs, fp32_tflops)
+
+    # the 90 % sparsity column of the sweep: 5 shapes x 3 widths
+    sweep = {}
+    for (M, K) in SHAPES:
+        for N in WIDTHS:
+            seed = 9000 + M + N
+            ro = pkg.gen_rowlen_normal_host(M, K, 0.9, COV, seed)
+            ci = pkg.gen_sample_columns_host(M, K, ro, seed)
+            nnz = int(ci.size)
+            Bm = torch.empty(K * N, device=dev)
+            ctx.gen_dense(Bm, seed, 10)
+            v = torch.empty(max(nnz, 1), device=dev)[:nnz]
+            ctx.gen_dense(v, seed, 2)
+            a = [v, up(ro), up(ci), Bm, torch.empty(M * N, device=dev)]
+            fn = lambda: ctx.spmm(M, K, N, nnz, *a)
+            fn(); fn()
+            sweep[f"{M}x{K}_n{N}"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+                                                spmm_bytes(M, K, N, nnz), hbm_gbs, fp32_tflops)
+    out["spmm_sweep_s0.9"] = sweep
+    del flush
+    return out
+
+
+def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
+    """One 65536 x 65536 SpMM at 1 % density, N = 512, rows sharded by nonzeros, C blocks gathered."""
+    import torch
+    import torch.distributed as dist
+
+    sharding = __import__("importlib").import_module(entry.PKG_NAME + ".sharding")
+    M = K = 65536
+    N = 512
+    density, seed = 0.01, 5
+    counts = torch.zeros(M, dtype=torch.int32, device=dev)
+    ctx.gen_bernoulli_count(M, K, density, seed, counts)
+    ro_all = np.zeros(M + 1, dtype=np.int32)
+    ro_all[1:] = np.cumsum(counts.cpu().numpy().astype(np.int64)).astype(np.int32)
+    r0, r1, bounds = sharding.row_block(pkg, ro_all, rank, world)
+    rows = r1 - r0
+    ro = torch.from_numpy(sharding.rebase_offsets(ro_all, r0, r1)).to(dev)
+    nnz = int(ro_all[r1] - ro_all[r0])
+    ci = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)[:nnz]
+    ctx.gen_bernoulli_fill(rows, K, density, seed, ro, ci, first_row=r0)
+    vals = torch.empty(max(nnz, 1), device=dev)[:nnz]
+    ctx.gen_dense(vals, seed, 2, first_index=int(ro_all[r0]))
+    B = torch.empty(K * N, device=dev)  # replicated on every rank
+    ctx.gen_dense(B, seed, 10)
+    Cl = torch.empty(rows, N, device=dev)
+    torch.cuda.synchronize()
+
+    def step():
+        ctx.spmm(rows, K, N, nnz, vals, ro, ci, B, Cl)
+        if world > 1:
+            return sharding.gather_row_blocks(Cl, bounds, N)
+        return Cl
+
+    step(); step()
+    torch.cuda.synchronize()
+    times, ktimes = [], []
+    for _ in range(reps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        ctx.spmm(rows, K, N, nnz, vals, ro, ci, B, Cl)
+        e1.record()
+        if world > 1:
+            sharding.gather_row_blocks(Cl, bounds, N)
+        e2.record()
+        e2.synchronize()
+        t = torch.tensor([e0.elapsed_time(e2), e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(float(t[0]))
+        ktimes.append(float(t[1]))
+    total_nnz = int(ro_all[-1])
+    flops = 2.0 * total_nnz * N
+    nbytes = spmm_bytes(M, K, N, total_nnz)
+    ms = statistics.median(times)
+    return {"workload": "65536x65536 density 0.01 N=512, rows sharded by nnz, B replicated, C all-gathered",
+            "ms_total_median": ms, "ms_kernel_median": statistics.median(ktimes), "gflops": flops / ms * 1e-6,
+            "hbm_frac": nbytes / ms * 1e-6 / hbm_gbs,
+            "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / ms,
+            "nnz": total_nnz, "n_gpus": world}
+
+
+# ---- main arm ------------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--problems", type=int, default=8192)
+    ap.add_argument("--seed", type=int, default=2024)
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-bytes", type=float, default=2e9, help="host bytes of the e2e sample per rank")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = entry.load_package()
+    ctx = pkg.Context(local_rank)
+    hbm_gbs, peak_kind = measured_peaks()
+    fp32_tflops = ctx.measure_fp32_peak()
+
+    t_setup = time.perf_counter()
+    descs = batch_descriptors(pkg, args.problems, args.seed)
+    weights = np.array([float(d[5][-1]) * d[2] for d in descs])
+    sharding = __import__("importlib").import_module(entry.PKG_NAME + ".sharding")
+    mine = sharding.my_problems(pkg, weights, rank, world)
+    batch = DeviceBatch(pkg, ctx, dev, descs, mine)
+    log(f"[rank {rank}] {len(mine)} problems, {batch.bytes_device / 2**30:.1f} GiB on device, "
+        f"{batch.flops / 1e12:.2f} TFLOP per step, set-up {time.perf_counter() - t_setup:.1f} s")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        batch.batch.launch()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for s in range(args.steps):
+        batch.batch.launch()
+        ev[s + 1].record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    my_ms = ev[0].elapsed_time(ev[-1])
+    launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    t = torch.tensor([my_ms], device=dev, dtype=torch.float64)
+    tot = torch.tensor([batch.flops, batch.alg_bytes], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    total_ms = float(t[0])
+    ms_per_step = total_ms / args.steps
+    value = float(tot[0]) / (ms_per_step * 1e-3) * 1e-9
+
+    # end to end through the host-buffer entry point (copies inside the timed region)
+    arr, keep, e_flops, e_h2d, e_d2h = batch.host_sample(int(args.e2e_bytes), 4096)
+    e_steps = max(3, min(args.steps, 5))
+    ctx.spmm_batched_host(arr)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e_steps):
+        ctx.spmm_batched_host(arr)
+    torch.cuda.synchronize()
+    e_dt = (time.perf_counter() - t0) / e_steps
+    et = torch.tensor([e_dt], device=dev, dtype=torch.float64)
+    ef = torch.tensor([e_flops, e_h2d, e_d2h], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(et, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ef, op=dist.ReduceOp.SUM)
+    e2e = {"value": float(ef[0]) / float(et[0]) * 1e-9, "unit": "GFLOP/s",
+           "h2d_bytes_per_step": float(ef[1]), "d2h_bytes_per_step": float(ef[2]),
+           "sample": f"first {len(keep)} problems of every rank's share, pinned host buffers, "
+                     "dlspm_spmm_batched_f32_host (H2D + grouped launch + D2H per step)",
+           "ms_per_step": float(et[0]) * 1e3}
+    del arr, keep
+
+    extras = {}
+    if not args.no_extras:
+        try:
+            extras["rowshard_65536"] = run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops)
+            if rank == 0 and world == 1:
+                extras.update(run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops))
+        except Exception as e:  # extras never invalidate the headline line
+            extras["error"] = repr(e)
+    barrier()
+
+    if rank == 0:
+        launch_avg_ms = statistics.mean(launch_ms)
+        achieved = batch.alg_bytes / (launch_avg_ms * 1e-3) * 1e-9
+        t_roof_ms = max(batch.alg_bytes / (hbm_gbs * 1e9), batch.flops / (fp32_tflops * 1e12)) * 1e3
+        line = {
+            "metric": "spmm_batch_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(args, world),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel": "spmm_batched_kernel", "launch_ms": launch_avg_ms,
+                         "algorithmic_bytes_per_launch": batch.alg_bytes,
+                         "fp32_peak_tflops_measured": fp32_tflops,
+                         "fp32_frac": batch.flops / (launch_avg_ms * 1e-3) * 1e-12 / fp32_tflops,
+                         "binding_roof": "hbm" if batch.alg_bytes / (hbm_gbs * 1e9) >= batch.flops / (fp32_tflops * 1e12) else "fp32",
+                         "roof_frac": t_roof_ms / launch_avg_ms},
+            "extras": extras,
+        }
+        if world == 1 and not args.no_cpu:
+            oracle = entry.load_oracle()
+            threads = oracle.max_threads()
+            rate = cpu_rate_probe(pkg, oracle, threads)
+            data, flops = cpu_sample(pkg, descs, rate * 1e9 * 15.0)
+            dt = time_cpu(oracle, data, threads)
+            line["cpu_baseline"] = {"value": flops / dt * 1e-9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"{len(data)} problems of the batch around the median cost "
+                                              f"({flops / 1e9:.2f} GFLOP, {dt:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -82,8 +82,8 @@ _SIGNATURES = {
     "dlspm_gen_sample_columns_host": (_I, [_I, _I, _P, C.c_uint64, _P]),
     "dlspm_gen_sample_columns": (_I, [_P, _I, _I, _P, C.c_uint64, _P, _P]),
     "dlspm_gen_band_csr_host": (_I, [_I, _I, _I, C.c_double, C.c_uint64, _P, _P, C.c_size_t, C.POINTER(_I)]),
-    "dlspm_gen_bernoulli_count": (_I, [_P, _I, _I, C.c_double, C.c_uint64, _P, _P]),
-    "dlspm_gen_bernoulli_fill": (_I, [_P, _I, _I, C.c_double, C.c_uint64, _P, _P, _P]),
+    "dlspm_gen_bernoulli_count": (_I, [_P, _I, _I, _I, C.c_double, C.c_uint64, _P, _P]),
+    "dlspm_gen_bernoulli_fill": (_I, [_P, _I, _I, _I, C.c_double, C.c_uint64, _P, _P, _P]),
     "dlspm_partition_lpt_host": (_I, [_I, _P, _I, _P]),
     "dlspm_partition_rows_by_nnz_host": (_I, [_I, _P, _I, _P]),
     "dlspm_mg_create": (_I, [C.POINTER(_P), _I, _P]),
@@ -314,18 +314,18 @@ class Context:
             _dev_ptr(column_indices, torch.int32, "column_indices"), _stream_ptr(stream)),
             "dlspm_gen_sample_columns", self)
 
-    def gen_bernoulli_count(self, M, K, density, seed, counts, stream=None) -> None:
+    def gen_bernoulli_count(self, M, K, density, seed, counts, stream=None, first_row=0) -> None:
         import torch
 
-        _check(self.lib.dlspm_gen_bernoulli_count(self.handle, M, K, density, seed,
+        _check(self.lib.dlspm_gen_bernoulli_count(self.handle, M, K, first_row, density, seed,
                                                   _dev_ptr(counts, torch.int32, "counts"), _stream_ptr(stream)),
                "dlspm_gen_bernoulli_count", self)
 
-    def gen_bernoulli_fill(self, M, K, density, seed, row_offsets, column_indices, stream=None) -> None:
+    def gen_bernoulli_fill(self, M, K, density, seed, row_offsets, column_indices, stream=None, first_row=0) -> None:
         import torch
 
         _check(self.lib.dlspm_gen_bernoulli_fill(
-            self.handle, M, K, density, seed, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
+            self.handle, M, K, first_row, density, seed, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
             _dev_ptr(column_indices, torch.int32, "column_indices"), _stream_ptr(stream)),
             "dlspm_gen_bernoulli_fill", self)
 

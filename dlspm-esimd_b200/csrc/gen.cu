@@ -140,11 +140,11 @@ gen_sample_columns_kernel(int M, int K, const int *__restrict__ row_offsets, uin
 }
 
 __global__ void __launch_bounds__(kGenThreads)
-gen_bernoulli_count_kernel(int M, int K, uint32_t thr, uint64_t key, int *__restrict__ counts)
+gen_bernoulli_count_kernel(int M, int K, int first_row, uint32_t thr, uint64_t key, int *__restrict__ counts)
 {
     __shared__ int warp_sums[kGenThreads / 32];
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
-        const uint64_t row_base = (uint64_t)row * (uint64_t)K;
+        const uint64_t row_base = (uint64_t)(first_row + row) * (uint64_t)K;
         int c = 0;
         for (int j = threadIdx.x; j < K; j += blockDim.x)
             c += dlspm_u24(dlspm_rng_at(key, row_base + (uint64_t)j)) < thr ? 1 : 0;
@@ -154,12 +154,12 @@ gen_bernoulli_count_kernel(int M, int K, uint32_t thr, uint64_t key, int *__rest
 }
 
 __global__ void __launch_bounds__(kGenThreads)
-gen_bernoulli_fill_kernel(int M, int K, uint32_t thr, uint64_t key, const int *__restrict__ row_offsets,
-                          int *__restrict__ cols)
+gen_bernoulli_fill_kernel(int M, int K, int first_row, uint32_t thr, uint64_t key,
+                          const int *__restrict__ row_offsets, int *__restrict__ cols)
 {
     __shared__ unsigned long long warp_sums64[kGenThreads / 32];
     for (int row = blockIdx.x; row < M; row += gridDim.x) {
-        const uint64_t row_base = (uint64_t)row * (uint64_t)K;
+        const uint64_t row_base = (uint64_t)(first_row + row) * (uint64_t)K;
         const int start = row_offsets[row];
         unsigned long long run = 0;
         for (int j0 = 0; j0 < K; j0 += blockDim.x) {
@@ -204,29 +204,30 @@ extern "C" int dlspm_gen_sample_columns(dlspm_ctx *ctx, int M, int K, const int 
     return DLSPM_OK;
 }
 
-extern "C" int dlspm_gen_bernoulli_count(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
-                                         int *row_counts, void *stream)
+extern "C" int dlspm_gen_bernoulli_count(dlspm_ctx *ctx, int M, int K, int first_row, double density,
+                                         uint64_t seed, int *row_counts, void *stream)
 {
-    if (!ctx || M < 0 || K < 0 || (M > 0 && !row_counts)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (!ctx || M < 0 || K < 0 || first_row < 0 || (M > 0 && !row_counts)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
     if (M == 0) return DLSPM_OK;
     gen_bernoulli_count_kernel<<<grid_for_rows(ctx, M), kGenThreads, 0, (cudaStream_t)stream>>>(
-        M, K, dlspm_density_threshold(density), dlspm_rng_key(seed, DLSPM_STREAM_PATTERN), row_counts);
+        M, K, first_row, dlspm_density_threshold(density), dlspm_rng_key(seed, DLSPM_STREAM_PATTERN), row_counts);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
 
-extern "C" int dlspm_gen_bernoulli_fill(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
-                                        const int *row_offsets, int *column_indices, void *stream)
+extern "C" int dlspm_gen_bernoulli_fill(dlspm_ctx *ctx, int M, int K, int first_row, double density,
+                                        uint64_t seed, const int *row_offsets, int *column_indices,
+                                        void *stream)
 {
-    if (!ctx || M < 0 || K < 0 || (M > 0 && !row_offsets)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (!ctx || M < 0 || K < 0 || first_row < 0 || (M > 0 && !row_offsets)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
     if (M == 0 || !column_indices) return DLSPM_OK;
     gen_bernoulli_fill_kernel<<<grid_for_rows(ctx, M), kGenThreads, 0, (cudaStream_t)stream>>>(
-        M, K, dlspm_density_threshold(density), dlspm_rng_key(seed, DLSPM_STREAM_PATTERN), row_offsets,
-        column_indices);
+        M, K, first_row, dlspm_density_threshold(density), dlspm_rng_key(seed, DLSPM_STREAM_PATTERN),
+        row_offsets, column_indices);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }

@@ -212,11 +212,14 @@ int dlspm_gen_sample_columns(dlspm_ctx *ctx, int M, int K, const int *row_offset
  * extras, sorted and without duplicates. */
 int dlspm_gen_band_csr_host(int M, int K, int half_band, double extra_density, uint64_t seed,
                             int *row_offsets, int *column_indices, size_t capacity, int *nnz);
-/* Device Bernoulli pattern in two steps: counts per row -> caller prefix-sums -> fill. */
-int dlspm_gen_bernoulli_count(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
-                              int *row_counts, void *stream);
-int dlspm_gen_bernoulli_fill(dlspm_ctx *ctx, int M, int K, double density, uint64_t seed,
-                             const int *row_offsets, int *column_indices, void *stream);
+/* Device Bernoulli pattern in two steps: counts per row -> caller prefix-sums -> fill.  The M rows
+ * generated are rows first_row .. first_row+M-1 of the K-column pattern of `seed`, so a row block
+ * of a large matrix can be produced on its own; row_offsets/row_counts are local to the block. */
+int dlspm_gen_bernoulli_count(dlspm_ctx *ctx, int M, int K, int first_row, double density,
+                              uint64_t seed, int *row_counts, void *stream);
+int dlspm_gen_bernoulli_fill(dlspm_ctx *ctx, int M, int K, int first_row, double density,
+                             uint64_t seed, const int *row_offsets, int *column_indices,
+                             void *stream);
 
 /* ---- partitioning for several GPUs (host, no CUDA) --------------------------------------- */
 
