@@ -62,6 +62,7 @@ _SIGNATURES = {
     "dlspm_plan_create": (_I, [_P, _I, _I, _I, _P, _P, _P, C.POINTER(_P)]),
     "dlspm_plan_destroy": (_I, [_P]),
     "dlspm_spmm_batched_f32": (_I, [_P, _I, C.POINTER(Problem), _P]),
+    "dlspm_spmm_batched_f32_static": (_I, [_P, _I, C.POINTER(Problem), _P]),
     "dlspm_batch_create": (_I, [_P, _I, C.POINTER(Problem), C.POINTER(_P)]),
     "dlspm_batch_launch": (_I, [_P, _P, _P]),
     "dlspm_batch_destroy": (_I, [_P]),
@@ -268,6 +269,12 @@ class Context:
     def spmm_batched(self, problems: "ProblemArray", stream=None) -> None:
         _check(self.lib.dlspm_spmm_batched_f32(self.handle, len(problems), problems.array, _stream_ptr(stream)),
                "dlspm_spmm_batched_f32", self)
+
+    def spmm_batched_static(self, problems: "ProblemArray", stream=None) -> None:
+        """Grouped launch that allocates nothing (tables in a fixed device array, <= 1024 problems)."""
+        _check(self.lib.dlspm_spmm_batched_f32_static(self.handle, len(problems), problems.array,
+                                                      _stream_ptr(stream)),
+               "dlspm_spmm_batched_f32_static", self)
 
     def batch_create(self, problems: "ProblemArray") -> "Batch":
         h = _P()

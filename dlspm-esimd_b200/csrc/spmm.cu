@@ -459,3 +459,111 @@ extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_pro
     return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
                                (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
 }
+
+// ---- grouped launch without any allocation ------------------------------------------------------
+// Some callers may not allocate device memory at the point where they need a grouped SpMM: a
+// plug-in running under a host framework that owns the device heap and hands out fixed buffers, a
+// real-time loop that must not take the allocator's lock, or code that runs after the heap has been
+// sized to the last byte.  dlspm_spmm_batched_f32 keeps its problem table, tile index and work
+// counter in context scratch that grows with cudaMalloc on demand; the variant below keeps them in
+// a fixed array that is part of the library image instead, so the call never allocates.  The price
+// is a hard limit on the batch size, and that every GPU which loads the library carries the array
+// (about 73 KiB) until the process exits.
+namespace {
+
+constexpr int kStaticMaxProblems = 1024;
+constexpr size_t kStaticTableBytes = sizeof(BatchProblem) * kStaticMaxProblems;
+constexpr size_t kStaticStartsOff = (kStaticTableBytes + 255) & ~(size_t)255;
+constexpr size_t kStaticStartsBytes = sizeof(long long) * (kStaticMaxProblems + 1);
+constexpr size_t kStaticCounterOff = (kStaticStartsOff + kStaticStartsBytes + 255) & ~(size_t)255;
+constexpr size_t kStaticScratchBytes = kStaticCounterOff + 256;
+
+// Problem table, tile index and work counter of dlspm_spmm_batched_f32_static.  In host code this
+// name is only a handle for cudaGetSymbolAddress, never an address a kernel can use.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices];  // device address of g_static_scratch, per device
+bool g_static_scratch_ready[kMaxDevices];
+
+// Looks up the device address of the static scratch on the context's device (which is current),
+// once per device.
+int static_scratch_address(dlspm_ctx *ctx, unsigned char **out)
+{
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return DLSPM_ERR_UNSUPPORTED;
+    if (!g_static_scratch_ready[ctx->device]) {
+        void *p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaGetSymbolAddress(g_static_scratch)");
+        g_static_scratch_addr[ctx->device] = p;
+        g_static_scratch_ready[ctx->device] = true;
+    }
+    *out = (unsigned char *)g_static_scratch_addr[ctx->device];
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                             void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (count > kStaticMaxProblems) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "dlspm_spmm_batched_f32_static: %d problems exceed the fixed limit of %d", count,
+                 kStaticMaxProblems);
+        return DLSPM_ERR_UNSUPPORTED;
+    }
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    unsigned char *base = nullptr;
+    rc = static_scratch_address(ctx, &base);
+    if (rc) return rc;
+
+    // Host tables on the stack (no heap either): same order as the allocating entry point,
+    // decreasing nnz*N with the lower index first on ties.
+    BatchProblem tab[kStaticMaxProblems];
+    long long starts[kStaticMaxProblems + 1];
+    int order[kStaticMaxProblems];
+    int used = 0;
+    for (int i = 0; i < count; i++) {
+        const dlspm_problem &q = problems[i];
+        rc = check_spmm_args(q.M, q.K, q.N, q.nnz, q.values, q.row_offsets, q.column_indices, q.B, q.C);
+        if (rc) return rc;
+        if (q.M > 0 && q.N > 0) order[used++] = i;
+    }
+    if (used == 0) return DLSPM_OK;
+    std::sort(order, order + used, [&](int x, int y) {
+        const double wx = (double)problems[x].nnz * problems[x].N, wy = (double)problems[y].nnz * problems[y].N;
+        return wx != wy ? wx > wy : x < y;
+    });
+    long long run = 0;
+    for (int s = 0; s < used; s++) {
+        const dlspm_problem &q = problems[order[s]];
+        BatchProblem &b = tab[s];
+        b.values = q.values;
+        b.row_offsets = q.row_offsets;
+        b.cols = q.column_indices;
+        b.B = q.B;
+        b.C = q.C;
+        b.M = q.M;
+        b.N = q.N;
+        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+        b.vec = dlspm_vec_width(q.N, q.B, q.C);
+        b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.pad = 0;
+        starts[s] = run;
+        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
+    }
+    starts[used] = run;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    BatchProblem *d_tab = (BatchProblem *)base;
+    long long *d_starts = (long long *)(base + kStaticStartsOff);
+    unsigned long long *d_counter = (unsigned long long *)(base + kStaticCounterOff);
+    // The array keeps what the previous call left in it: the tables are overwritten here and the
+    // work counter is cleared by batch_launch_tables before the kernel starts.
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_tab, tab, sizeof(BatchProblem) * (size_t)used, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_starts, starts, sizeof(long long) * ((size_t)used + 1), cudaMemcpyHostToDevice, st));
+    return batch_launch_tables(ctx, d_tab, d_starts, d_counter, used, run, st);
+}

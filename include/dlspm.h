@@ -135,6 +135,18 @@ typedef struct dlspm_problem {
 int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                            void *stream);
 
+/* The same grouped launch for callers that must not allocate device memory (a plug-in whose host
+ * owns the device heap, a loop that may not take the allocator's lock).  This entry point has no
+ * counterpart in the reference.  It never calls cudaMalloc/cudaFree or any allocating routine: its
+ * problem table, tile index and work counter live in a fixed __device__ array inside the library
+ * (about 73 KiB per GPU, held until the process exits).  Limit: count <= 1024 problems, otherwise
+ * DLSPM_ERR_UNSUPPORTED.  The first call on a device looks up the array's device address; make
+ * that call before any stream capture.  All calls on a device share the one array, so two calls
+ * whose work overlaps on the GPU (different streams, no ordering) race; calls on one stream are
+ * safe.  Results are identical to dlspm_spmm_batched_f32. */
+int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                  void *stream);
+
 /* A prepared batch: the problem table and its tile index live on the device, so repeated
  * launches cost no host work. */
 typedef struct dlspm_batch dlspm_batch;
