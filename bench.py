@@ -300,6 +300,34 @@ def workload_config(args, world):
 
 # ---- extras: the other configurations ---------------------------------------------------------------------------
 
+def time_graph(fn, inner=20, reps=5):
+    """Warm per-launch time in ms: `inner` back-to-back launches captured in one CUDA graph, so that
+    host launch latency (about 10 us per call from Python) does not sit between the events."""
+    import torch
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(inner):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) / inner)
+    return times
+
+
 def time_kernel(fn, reps, flush=None):
     """Per-launch device times in ms (CUDA events on the current stream)."""
     import torch
@@ -343,7 +371,7 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
     d = [up(pkg.gen_dense_host(nnz, 1, 2)), up(ro), up(ci), up(pkg.gen_dense_host(K * N, 1, 10)), torch.empty(M * N, device=dev)]
     fn = lambda: ctx.spmm(M, K, N, nnz, *d)
     fn(); fn()
-    out["spmm_512x512_d0.1_n128"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+    out["spmm_512x512_d0.1_n128"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 2.0 * nnz * N,
                                                spmm_bytes(M, K, N, nnz), hbm_gbs, fp32_tflops)
 
     # SDDMM 2048 x 512 mask at density 0.2, inner dimension 128
@@ -354,7 +382,7 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
          torch.empty(nnz, device=dev)]
     fn = lambda: ctx.sddmm(M, K, N, nnz, *s)
     fn(); fn()
-    out["sddmm_2048x512_d0.2_n128"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+    out["sddmm_2048x512_d0.2_n128"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 2.0 * nnz * N,
                                                  4 * (M + 1) + 8 * nnz + 4 * M * N + 4 * K * N, hbm_gbs, fp32_tflops)
 
     # fused SDDMM -> SpMM, band(64) + 5 % mask 4096 x 4096, d = 64
@@ -366,7 +394,7 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
          up(pkg.gen_dense_host(K * N, 4, 13, kind=2)), torch.empty(M * N, device=dev)]
     fn = lambda: ctx.fused(M, K, N, nnz, *f)
     fn(); fn()
-    out["fused_band4096_d64"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 4.0 * nnz * N,
+    out["fused_band4096_d64"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 4.0 * nnz * N,
                                           4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N, hbm_gbs, fp32_tflops)
 
     # the 90 % sparsity column of the sweep: 5 shapes x 3 widths
@@ -384,7 +412,7 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
             a = [v, up(ro), up(ci), Bm, torch.empty(M * N, device=dev)]
             fn = lambda: ctx.spmm(M, K, N, nnz, *a)
             fn(); fn()
-            sweep[f"{M}x{K}_n{N}"] = summarize(time_kernel(fn, reps), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+            sweep[f"{M}x{K}_n{N}"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 2.0 * nnz * N,
                                                 spmm_bytes(M, K, N, nnz), hbm_gbs, fp32_tflops)
     out["spmm_sweep_s0.9"] = sweep
     del flush
@@ -466,6 +494,8 @@ def main():
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tile-density", type=int, default=None, help="DLSPM_OPT_TILE_MIN_DENSITY in thousandths")
+    ap.add_argument("--spmm-kernel", type=int, default=0, help="0 auto, 1 row-gather only, 2 tiled where possible")
     ap.add_argument("--e2e-bytes", type=float, default=2e9, help="host bytes of the e2e sample per rank")
     args = ap.parse_args()
 
@@ -489,6 +519,9 @@ def main():
 
     pkg = entry.load_package()
     ctx = pkg.Context(local_rank)
+    if args.tile_density is not None:
+        ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, args.tile_density)
+    ctx.set_option(pkg.OPT_SPMM_KERNEL, args.spmm_kernel)
     hbm_gbs, peak_kind = measured_peaks()
     fp32_tflops = ctx.measure_fp32_peak()
 
@@ -498,7 +531,11 @@ def main():
     sharding = __import__("importlib").import_module(entry.PKG_NAME + ".sharding")
     mine = sharding.my_problems(pkg, weights, rank, world)
     batch = DeviceBatch(pkg, ctx, dev, descs, mine)
-    log(f"[rank {rank}] {len(mine)} problems, {batch.bytes_device / 2**30:.1f} GiB on device, "
+    n_gather, n_tiled, _ = batch.batch.info()
+    part_stats = list(batch.batch.stats)
+    launches_per_step = (1 if n_gather else 0) + (1 if n_tiled else 0)
+    log(f"[rank {rank}] {len(mine)} problems ({n_tiled} tiled, {n_gather} row-gather), "
+        f"{batch.bytes_device / 2**30:.1f} GiB on device, "
         f"{batch.flops / 1e12:.2f} TFLOP per step, set-up {time.perf_counter() - t_setup:.1f} s")
 
     def barrier():
@@ -527,6 +564,26 @@ def main():
     total_ms = float(t[0])
     ms_per_step = total_ms / args.steps
     value = float(tot[0]) / (ms_per_step * 1e-3) * 1e-9
+
+    # each kernel of the step on its own (rank 0's share), for the roofline of the dominant one
+    parts = {}
+    for part, name, nprob, fl, by in ((1, "spmm_batched_kernel", n_gather, part_stats[0], part_stats[1]),
+                                      (2, "spmm_tile_kernel", n_tiled, part_stats[2], part_stats[3])):
+        if not nprob:
+            continue
+        batch.batch.launch_part(part)
+        torch.cuda.synchronize()
+        pe = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        pe[0].record()
+        for i in range(3):
+            batch.batch.launch_part(part)
+            pe[i + 1].record()
+        torch.cuda.synchronize()
+        ms = statistics.mean(pe[i].elapsed_time(pe[i + 1]) for i in range(3))
+        parts[name] = {"problems": nprob, "launch_ms": ms, "gflops": fl / ms * 1e-6,
+                       "algorithmic_bytes_per_launch": by, "achieved_gbs": by / ms * 1e-6,
+                       "fp32_frac": fl / (ms * 1e-3) * 1e-12 / fp32_tflops}
+    barrier()
 
     # end to end through the host-buffer entry point (copies inside the timed region)
     arr, keep, e_flops, e_h2d, e_d2h = batch.host_sample(int(args.e2e_bytes), 4096)
@@ -561,23 +618,28 @@ def main():
     barrier()
 
     if rank == 0:
-        launch_avg_ms = statistics.mean(launch_ms)
-        achieved = batch.alg_bytes / (launch_avg_ms * 1e-3) * 1e-9
-        t_roof_ms = max(batch.alg_bytes / (hbm_gbs * 1e9), batch.flops / (fp32_tflops * 1e12)) * 1e3
+        step_avg_ms = statistics.mean(launch_ms)
+        dominant = max(parts, key=lambda k: parts[k]["launch_ms"])
+        dom = parts[dominant]
+        launch_avg_ms = dom["launch_ms"]
+        achieved = dom["achieved_gbs"]
+        dom_flops = dom["gflops"] * 1e6 * dom["launch_ms"]
+        t_roof_ms = max(dom["algorithmic_bytes_per_launch"] / (hbm_gbs * 1e9), dom_flops / (fp32_tflops * 1e12)) * 1e3
         line = {
             "metric": "spmm_batch_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args, world),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
                          "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"of {peak_kind}",
-                         "kernel": "spmm_batched_kernel", "launch_ms": launch_avg_ms,
-                         "algorithmic_bytes_per_launch": batch.alg_bytes,
+                         "kernel": dominant, "launch_ms": launch_avg_ms,
+                         "algorithmic_bytes_per_launch": dom["algorithmic_bytes_per_launch"],
                          "fp32_peak_tflops_measured": fp32_tflops,
-                         "fp32_frac": batch.flops / (launch_avg_ms * 1e-3) * 1e-12 / fp32_tflops,
-                         "binding_roof": "hbm" if batch.alg_bytes / (hbm_gbs * 1e9) >= batch.flops / (fp32_tflops * 1e12) else "fp32",
-                         "roof_frac": t_roof_ms / launch_avg_ms},
+                         "fp32_frac": dom["fp32_frac"],
+                         "binding_roof": "hbm" if dom["algorithmic_bytes_per_launch"] / (hbm_gbs * 1e9) >= dom_flops / (fp32_tflops * 1e12) else "fp32",
+                         "roof_frac": t_roof_ms / launch_avg_ms,
+                         "step_ms_rank0": step_avg_ms, "kernels": parts},
             "extras": extras,
         }
         if world == 1 and not args.no_cpu:

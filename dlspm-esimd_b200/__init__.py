@@ -22,8 +22,10 @@ LIB_PATH = os.path.join(PKG_DIR, "libdlspm.so")
 HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "dlspm.h")
 
 OK = 0
-ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_IO, ERR_FORMAT, ERR_CSR, ERR_NOMEM, ERR_UNSUPPORTED, ERR_NO_DEVICE = range(1, 9)
-OPT_STRICT_FP32, OPT_SPMM_KERNEL = 0, 1
+(ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_IO, ERR_FORMAT, ERR_CSR, ERR_NOMEM, ERR_UNSUPPORTED, ERR_NO_DEVICE,
+ ERR_TIMEOUT) = range(1, 10)
+OPT_STRICT_FP32, OPT_SPMM_KERNEL, OPT_TILE_MIN_DENSITY = 0, 1, 2
+SPMM_KERNEL_AUTO, SPMM_KERNEL_GATHER, SPMM_KERNEL_TILED = 0, 1, 2
 KIND_UNIFORM_PM1, KIND_UNIFORM_01, KIND_NORMAL = 0, 1, 2
 
 
@@ -65,6 +67,8 @@ _SIGNATURES = {
     "dlspm_spmm_batched_f32_static": (_I, [_P, _I, C.POINTER(Problem), _P]),
     "dlspm_batch_create": (_I, [_P, _I, C.POINTER(Problem), C.POINTER(_P)]),
     "dlspm_batch_launch": (_I, [_P, _P, _P]),
+    "dlspm_batch_launch_part": (_I, [_P, _P, _I, _P]),
+    "dlspm_batch_info": (_I, [_P, _P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(C.c_double)]),
     "dlspm_batch_destroy": (_I, [_P]),
     "dlspm_spmm_csr_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "dlspm_sddmm_csr_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
@@ -402,6 +406,20 @@ class Batch:
     def launch(self, stream=None) -> None:
         _check(self.ctx.lib.dlspm_batch_launch(self.ctx.handle, self.handle, _stream_ptr(stream)),
                "dlspm_batch_launch", self.ctx)
+
+    def info(self, check_device: bool = False):
+        """(problems on the row-gather kernel, problems on the tiled kernel, device error word or None)."""
+        g, t, e = _I(), _I(), _I()
+        self.stats = (C.c_double * 4)()
+        _check(self.ctx.lib.dlspm_batch_info(self.ctx.handle, self.handle, C.byref(g), C.byref(t),
+                                             C.byref(e) if check_device else None, self.stats),
+               "dlspm_batch_info", self.ctx)
+        return g.value, t.value, (e.value if check_device else None)
+
+    def launch_part(self, part: int, stream=None) -> None:
+        """1 = row-gather problems only, 2 = tiled problems only, 0 = all."""
+        _check(self.ctx.lib.dlspm_batch_launch_part(self.ctx.handle, self.handle, part, _stream_ptr(stream)),
+               "dlspm_batch_launch_part", self.ctx)
 
     def close(self) -> None:
         if self.handle:

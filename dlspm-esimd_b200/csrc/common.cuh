@@ -15,6 +15,7 @@ struct dlspm_ctx {
     char last_error[512];
     int strict_fp32;  // DLSPM_OPT_STRICT_FP32
     int spmm_kernel;  // DLSPM_OPT_SPMM_KERNEL
+    int tile_min_density_permille;  // DLSPM_OPT_TILE_MIN_DENSITY
     // Device scratch owned by the context, grown on demand (grouped-launch tables, staging for
     // the host-buffer entry points).  Freed in dlspm_destroy.
     void *scratch;

@@ -26,6 +26,7 @@ extern "C" const char *dlspm_strerror(int status)
     case DLSPM_ERR_NOMEM: return "out of memory";
     case DLSPM_ERR_UNSUPPORTED: return "size beyond a documented limit";
     case DLSPM_ERR_NO_DEVICE: return "no usable CUDA device";
+    case DLSPM_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
     default: return "unknown status";
     }
 }
@@ -44,6 +45,7 @@ extern "C" int dlspm_create(dlspm_ctx **out, int device)
     if (!ctx) return DLSPM_ERR_NOMEM;
     memset(ctx, 0, sizeof(*ctx));
     ctx->device = device;
+    ctx->tile_min_density_permille = 1001;  // tiled kernel only on request until it beats row-gather
     cudaDeviceProp prop;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -100,6 +102,10 @@ extern "C" int dlspm_set_option(dlspm_ctx *ctx, int option, int value)
         if (value < 0 || value > 2) return DLSPM_ERR_INVALID_ARGUMENT;
         ctx->spmm_kernel = value;
         return DLSPM_OK;
+    case DLSPM_OPT_TILE_MIN_DENSITY:
+        if (value < 0 || value > 1001) return DLSPM_ERR_INVALID_ARGUMENT;
+        ctx->tile_min_density_permille = value;
+        return DLSPM_OK;
     default: return DLSPM_ERR_INVALID_ARGUMENT;
     }
 }
@@ -110,6 +116,7 @@ extern "C" int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value)
     switch (option) {
     case DLSPM_OPT_STRICT_FP32: *value = ctx->strict_fp32; return DLSPM_OK;
     case DLSPM_OPT_SPMM_KERNEL: *value = ctx->spmm_kernel; return DLSPM_OK;
+    case DLSPM_OPT_TILE_MIN_DENSITY: *value = ctx->tile_min_density_permille; return DLSPM_OK;
     default: return DLSPM_ERR_INVALID_ARGUMENT;
     }
 }

@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "spmm_device.cuh"
+#include "spmm_tile.cuh"
 
 using namespace dlspm;
 
@@ -24,6 +25,7 @@ struct SpmmArgs {
     const int *row_order;  // nullptr = natural order
     int M, N;
     int row_groups;  // ceil(M / 8)
+    int chunks;      // column chunks per slab (<= compiled U)
 };
 
 template <int VEC, int U, bool STRICT>
@@ -39,8 +41,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const Spmm
     const int row = a.row_order ? a.row_order[slot] : slot;
     const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
     spmm_warp_row_slab<VEC, U, STRICT>(a.values, a.cols, start, end, a.B,
-                                       a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * U, lane,
-                                       stage[warp]);
+                                       a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * a.chunks,
+                                       a.chunks, lane, stage[warp]);
 }
 
 template <int VEC, int U>
@@ -53,10 +55,11 @@ void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
 }
 
 template <int VEC>
-void launch_rows_vec(const SpmmArgs &a, bool strict, cudaStream_t st)
+void launch_rows_vec(SpmmArgs a, bool strict, cudaStream_t st)
 {
-    const int U = spmm_slab_chunks(a.N, VEC);
-    const int slabs = dlspm_ceil_div(a.N, 32 * VEC * U);
+    a.chunks = spmm_slab_chunks(a.N, VEC);
+    const int slabs = dlspm_ceil_div(a.N, 32 * VEC * a.chunks);
+    const int U = a.chunks;
     if (U == 4) launch_rows<VEC, 4>(a, slabs, strict, st);
     else if (U == 2) launch_rows<VEC, 2>(a, slabs, strict, st);
     else launch_rows<VEC, 1>(a, slabs, strict, st);
@@ -76,7 +79,7 @@ int spmm_launch(dlspm_ctx *ctx, int M, int N, const float *values, const int *ro
                 const int *cols, const float *B, float *C, const int *row_order, cudaStream_t st)
 {
     if (M == 0 || N == 0) return DLSPM_OK;
-    SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta)};
+    SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1};
     const int vec = dlspm_vec_width(N, B, C);
     const bool strict = ctx->strict_fp32 != 0;
     if (vec == 4) launch_rows_vec<4>(a, strict, st);
@@ -252,7 +255,10 @@ struct BatchProblem {
     int M, N;
     int row_groups;
     int vec;     // 1, 2 or 4
-    int chunks;  // U: 1, 2 or 4
+    int chunks;  // column chunks per slab: 1, 2 or 4
+    int K;
+    const int *row_order;  // rows from the longest to the shortest (nullptr: natural order)
+    int nnz;
     int pad;
 };
 
@@ -261,12 +267,13 @@ __device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, in
                                              int end, int lane, int2 *stage)
 {
     float *Crow = p.C + (size_t)row * (size_t)p.N;
+    const int n0 = slab * 32 * VEC * p.chunks;
     if (p.chunks == 4)
-        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 128 * VEC, lane, stage);
+        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
     else if (p.chunks == 2)
-        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 64 * VEC, lane, stage);
+        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
     else
-        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, slab * 32 * VEC, lane, stage);
+        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
 }
 
 // Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
@@ -296,8 +303,9 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
         const BatchProblem p = problems[lo];
         const long long t = tile - __ldg(tile_start + lo);
         const int slab = (int)(t / p.row_groups);
-        const int row = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
-        if (row < p.M) {
+        const int slot = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
+        if (slot < p.M) {
+            const int row = p.row_order ? __ldg(p.row_order + slot) : slot;
             const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
             if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage[warp]);
             else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage[warp]);
@@ -307,15 +315,6 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
 }
 
 }  // namespace
-
-struct dlspm_batch {
-    dlspm_ctx *ctx;
-    int count;        // problems with at least one tile
-    long long tiles;
-    BatchProblem *problems;  // device
-    long long *tile_start;   // device, count + 1
-    unsigned long long *counter;  // device
-};
 
 namespace {
 
@@ -351,6 +350,9 @@ int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProb
         b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
         b.vec = dlspm_vec_width(q.N, q.B, q.C);
         b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.K = q.K;
+        b.row_order = nullptr;
+        b.nnz = q.nnz;
         b.pad = 0;
         starts.push_back(run);
         run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
@@ -359,6 +361,90 @@ int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProb
     starts.push_back(run);
     return DLSPM_OK;
 }
+
+}  // namespace
+
+// ---- analysis of a batch: row order by length and sortedness, one thread block per problem -------
+namespace {
+
+constexpr int kLenBins = 4096;  // counting sort on min(row length, 4095)
+
+// flags[i] bit 0: every row of problem i has strictly ascending columns.
+__global__ void __launch_bounds__(256) batch_analyze_kernel(const BatchProblem *__restrict__ problems, int count,
+                                                           int *__restrict__ flags)
+{
+    __shared__ int hist[kLenBins];
+    __shared__ int warp_tot[8];
+    __shared__ int s_sorted;
+    for (int pi = blockIdx.x; pi < count; pi += gridDim.x) {
+        const BatchProblem p = problems[pi];
+        for (int b = threadIdx.x; b < kLenBins; b += blockDim.x) hist[b] = 0;
+        if (threadIdx.x == 0) s_sorted = 1;
+        __syncthreads();
+        bool sorted = true;
+        for (int r = threadIdx.x; r < p.M; r += blockDim.x) {
+            const int s = p.row_offsets[r], e = p.row_offsets[r + 1];
+            atomicAdd(&hist[min(max(e - s, 0), kLenBins - 1)], 1);
+            for (int q = s + 1; q < e; q++) sorted &= p.cols[q - 1] < p.cols[q];
+        }
+        if (!sorted) s_sorted = 0;
+        __syncthreads();
+        // exclusive scan over the bins from the longest to the shortest: 16 bins per thread
+        const int per = kLenBins / 256;
+        int local[per];
+        int sum = 0;
+        for (int i = 0; i < per; i++) {
+            local[i] = hist[kLenBins - 1 - (threadIdx.x * per + i)];
+            sum += local[i];
+        }
+        int incl = sum;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((threadIdx.x & 31) >= d) incl += o;
+        }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        int before = incl - sum;
+        for (int w = 0; w < (int)(threadIdx.x >> 5); w++) before += warp_tot[w];
+        __syncthreads();
+        for (int i = 0; i < per; i++) {
+            hist[kLenBins - 1 - (threadIdx.x * per + i)] = before;  // first slot of the bin
+            before += local[i];
+        }
+        __syncthreads();
+        if (p.row_order) {
+            int *order = const_cast<int *>(p.row_order);
+            for (int r = threadIdx.x; r < p.M; r += blockDim.x) {
+                const int len = p.row_offsets[r + 1] - p.row_offsets[r];
+                order[atomicAdd(&hist[min(max(len, 0), kLenBins - 1)], 1)] = r;
+            }
+        }
+        if (threadIdx.x == 0) flags[pi] = s_sorted;
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+struct dlspm_batch {
+    dlspm_ctx *ctx;
+    // row-gather part
+    int count;
+    long long tiles;
+    BatchProblem *problems;       // device
+    long long *tile_start;        // device, count + 1
+    // tiled part (denser problems)
+    int tcount;
+    long long ttiles;
+    TileProblem *tproblems;       // device
+    long long *ttile_start;       // device, tcount + 1
+    unsigned long long *counters; // device: [0] row-gather, [1] tiled
+    int *row_order_pool;          // device: row orders of all row-gather problems
+    int *error;                   // device: set by a kernel whose bounded wait ran out
+    double stats[4];              // 2*nnz*N and algorithmic bytes: row-gather part, tiled part
+};
+
+namespace {
 
 int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long long *d_starts,
                         unsigned long long *d_counter, int count, long long tiles, cudaStream_t st)
@@ -373,6 +459,37 @@ int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long lo
     return DLSPM_OK;
 }
 
+int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long *d_starts,
+                       unsigned long long *d_counter, int *d_error, int count, long long tiles, cudaStream_t st)
+{
+    if (count == 0 || tiles == 0) return DLSPM_OK;
+    static bool attr_set[64];
+    const size_t smem = sizeof(TileSmem);
+    if (ctx->device < 64 && !attr_set[ctx->device]) {
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[ctx->device] = true;
+    }
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 2);
+    dim3 grid((unsigned)want), block(kTileThreads);
+    if (ctx->strict_fp32) spmm_tile_kernel<true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    else spmm_tile_kernel<false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+// Kernel choice for one problem of a prepared batch.  The tiled kernel needs 16-byte aligned rows
+// of B and C (N % 4 == 0) and strictly ascending columns; it pays off once a B row loaded into shared
+// memory is used by more than one of a warp's 8 rows often enough, i.e. from a density threshold.
+bool prefer_tiled(const dlspm_ctx *ctx, const dlspm_problem &q, int vec, bool sorted)
+{
+    if (ctx->spmm_kernel == 1 || vec != 4 || !sorted || q.nnz == 0) return false;
+    if (ctx->spmm_kernel == 2) return true;
+    const double density = (double)q.nnz / ((double)q.M * (double)q.K);
+    return density * 1000.0 >= (double)ctx->tile_min_density_permille && q.M >= 16 && q.N >= 64;
+}
+
 }  // namespace
 
 extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
@@ -384,24 +501,94 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     if (rc) return rc;
     std::vector<BatchProblem> tab;
     std::vector<long long> starts;
-    rc = build_tables(count, problems, tab, starts);
+    rc = build_tables(count, problems, tab, starts);  // validates; all problems, most work first
     if (rc) return rc;
     dlspm_batch *b = new (std::nothrow) dlspm_batch();
     if (!b) return DLSPM_ERR_NOMEM;
+    memset(b, 0, sizeof(*b));
     b->ctx = ctx;
-    b->count = (int)tab.size();
-    b->tiles = starts.back();
-    b->problems = nullptr;
-    b->tile_start = nullptr;
-    b->counter = nullptr;
-    const size_t tab_bytes = sizeof(BatchProblem) * std::max<size_t>(tab.size(), 1);
-    const size_t st_bytes = sizeof(long long) * starts.size();
-    cudaError_t err = cudaMalloc(&b->problems, tab_bytes);
-    if (err == cudaSuccess) err = cudaMalloc(&b->tile_start, st_bytes);
-    if (err == cudaSuccess) err = cudaMalloc(&b->counter, sizeof(unsigned long long));
-    if (err == cudaSuccess && !tab.empty())
-        err = cudaMemcpy(b->problems, tab.data(), sizeof(BatchProblem) * tab.size(), cudaMemcpyHostToDevice);
-    if (err == cudaSuccess) err = cudaMemcpy(b->tile_start, starts.data(), st_bytes, cudaMemcpyHostToDevice);
+    const size_t n = tab.size();
+    // pass 1: analyse every problem on the device (row order by length, sortedness)
+    size_t rows_total = 0;
+    for (const BatchProblem &t : tab) rows_total += (size_t)t.M;
+    int *d_flags = nullptr;
+    BatchProblem *d_all = nullptr;
+    std::vector<int> flags(n, 0);
+    cudaError_t err = cudaMalloc(&b->row_order_pool, sizeof(int) * std::max<size_t>(rows_total, 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->counters, 2 * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMalloc(&b->error, sizeof(int));
+    if (err == cudaSuccess) err = cudaMemset(b->error, 0, sizeof(int));
+    if (err == cudaSuccess && n) {
+        size_t off = 0;
+        for (BatchProblem &t : tab) {
+            t.row_order = b->row_order_pool + off;
+            off += (size_t)t.M;
+        }
+        err = cudaMalloc(&d_all, sizeof(BatchProblem) * n);
+        if (err == cudaSuccess) err = cudaMalloc(&d_flags, sizeof(int) * n);
+        if (err == cudaSuccess) err = cudaMemcpy(d_all, tab.data(), sizeof(BatchProblem) * n, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) {
+            const int blocks = (int)std::min<size_t>(n, (size_t)ctx->sm_count * 8);
+            batch_analyze_kernel<<<blocks, 256>>>(d_all, (int)n, d_flags);
+            err = cudaMemcpy(flags.data(), d_flags, sizeof(int) * n, cudaMemcpyDeviceToHost);
+        }
+        if (d_flags) cudaFree(d_flags);
+        if (d_all) cudaFree(d_all);
+    }
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "batch analysis");
+        dlspm_batch_destroy(b);
+        return DLSPM_ERR_CUDA;
+    }
+    // pass 2: split into the tiled and the row-gather tables
+    std::vector<BatchProblem> gtab;
+    std::vector<long long> gstarts;
+    std::vector<TileProblem> ttab;
+    std::vector<long long> tstarts;
+    long long grun = 0, trun = 0;
+    for (size_t i = 0; i < n; i++) {
+        const BatchProblem &t = tab[i];
+        dlspm_problem q;
+        q.M = t.M; q.K = t.K; q.N = t.N;
+        q.nnz = t.nnz;
+        const double fl = 2.0 * (double)t.nnz * t.N;
+        const double by = 4.0 * (t.M + 1) + 8.0 * t.nnz + 4.0 * (double)t.K * t.N + 4.0 * (double)t.M * t.N;
+        const bool tiled = prefer_tiled(ctx, q, t.vec, flags[i] & 1);
+        b->stats[tiled ? 2 : 0] += fl;
+        b->stats[tiled ? 3 : 1] += by;
+        if (tiled) {
+            TileProblem tp;
+            tp.values = t.values; tp.row_offsets = t.row_offsets; tp.cols = t.cols; tp.B = t.B; tp.C = t.C;
+            tp.row_order = t.row_order;
+            tp.M = t.M; tp.K = t.K; tp.N = t.N;
+            tp.row_blocks = dlspm_ceil_div(t.M, kTileM);
+            tp.col_blocks = dlspm_ceil_div(t.N, kTileN);
+            tp.pad = 0;
+            tstarts.push_back(trun);
+            trun += (long long)tp.row_blocks * tp.col_blocks;
+            ttab.push_back(tp);
+        } else {
+            gstarts.push_back(grun);
+            grun += (long long)t.row_groups * dlspm_ceil_div(t.N, 32 * t.vec * t.chunks);
+            gtab.push_back(t);
+        }
+    }
+    gstarts.push_back(grun);
+    tstarts.push_back(trun);
+    b->count = (int)gtab.size();
+    b->tiles = grun;
+    b->tcount = (int)ttab.size();
+    b->ttiles = trun;
+    err = cudaMalloc(&b->problems, sizeof(BatchProblem) * std::max<size_t>(gtab.size(), 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->tile_start, sizeof(long long) * gstarts.size());
+    if (err == cudaSuccess) err = cudaMalloc(&b->tproblems, sizeof(TileProblem) * std::max<size_t>(ttab.size(), 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->ttile_start, sizeof(long long) * tstarts.size());
+    if (err == cudaSuccess && !gtab.empty())
+        err = cudaMemcpy(b->problems, gtab.data(), sizeof(BatchProblem) * gtab.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(b->tile_start, gstarts.data(), sizeof(long long) * gstarts.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess && !ttab.empty())
+        err = cudaMemcpy(b->tproblems, ttab.data(), sizeof(TileProblem) * ttab.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(b->ttile_start, tstarts.data(), sizeof(long long) * tstarts.size(), cudaMemcpyHostToDevice);
     if (err != cudaSuccess) {
         dlspm_cuda_fail(ctx, err, "batch tables");
         dlspm_batch_destroy(b);
@@ -411,13 +598,44 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     return DLSPM_OK;
 }
 
+extern "C" int dlspm_batch_launch_part(dlspm_ctx *ctx, const dlspm_batch *batch, int part, void *stream)
+{
+    if (!ctx || !batch || batch->ctx != ctx || part < 0 || part > 2) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (part != 1) {
+        rc = tile_launch_tables(ctx, batch->tproblems, batch->ttile_start, batch->counters + 1, batch->error,
+                                batch->tcount, batch->ttiles, st);
+        if (rc) return rc;
+    }
+    if (part != 2) {
+        rc = batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counters, batch->count,
+                                 batch->tiles, st);
+    }
+    return rc;
+}
+
 extern "C" int dlspm_batch_launch(dlspm_ctx *ctx, const dlspm_batch *batch, void *stream)
+{
+    return dlspm_batch_launch_part(ctx, batch, 0, stream);
+}
+
+// Number of problems served by each kernel (for reports) and the device-side error word.
+extern "C" int dlspm_batch_info(dlspm_ctx *ctx, const dlspm_batch *batch, int *gather_problems,
+                                int *tiled_problems, int *device_error, double *stats4)
 {
     if (!ctx || !batch || batch->ctx != ctx) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
-    return batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counter, batch->count,
-                               batch->tiles, (cudaStream_t)stream);
+    if (gather_problems) *gather_problems = batch->count;
+    if (tiled_problems) *tiled_problems = batch->tcount;
+    if (stats4) memcpy(stats4, batch->stats, sizeof(batch->stats));
+    if (device_error) {
+        DLSPM_CUDA_TRY(ctx, cudaDeviceSynchronize());
+        DLSPM_CUDA_TRY(ctx, cudaMemcpy(device_error, batch->error, sizeof(int), cudaMemcpyDeviceToHost));
+    }
+    return DLSPM_OK;
 }
 
 extern "C" int dlspm_batch_destroy(dlspm_batch *b)
@@ -426,7 +644,11 @@ extern "C" int dlspm_batch_destroy(dlspm_batch *b)
     cudaSetDevice(b->ctx->device);
     if (b->problems) cudaFree(b->problems);
     if (b->tile_start) cudaFree(b->tile_start);
-    if (b->counter) cudaFree(b->counter);
+    if (b->tproblems) cudaFree(b->tproblems);
+    if (b->ttile_start) cudaFree(b->ttile_start);
+    if (b->counters) cudaFree(b->counters);
+    if (b->row_order_pool) cudaFree(b->row_order_pool);
+    if (b->error) cudaFree(b->error);
     (void)cudaGetLastError();
     delete b;
     return DLSPM_OK;
@@ -551,6 +773,9 @@ extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dl
         b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
         b.vec = dlspm_vec_width(q.N, q.B, q.C);
         b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.K = q.K;
+        b.row_order = nullptr;
+        b.nnz = q.nnz;
         b.pad = 0;
         starts[s] = run;
         run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);

@@ -49,18 +49,21 @@ __device__ __forceinline__ float mad(float a, float b, float c)
     else return fmaf(a, b, c);
 }
 
-// stage: 32 int2 slots private to this warp.
+// stage: 32 int2 slots private to this warp.  U is the compiled number of column chunks per lane;
+// `chunks` (<= U) is how many of them this slab really has, so that the slab width can be any
+// multiple of 32*VEC up to 32*VEC*U (3136 columns are 5 slabs of 5 chunks, not 7 slabs of 4).
 template <int VEC, int U, bool STRICT>
 __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
                                                    const int *__restrict__ cols, int start, int end,
                                                    const float *__restrict__ B, float *__restrict__ Crow,
-                                                   int N, int n0, int lane, int2 *stage)
+                                                   int N, int n0, int chunks, int lane, int2 *stage)
 {
     float acc[U][VEC];
     int cidx[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
-        cidx[u] = n0 + (u * 32 + lane) * VEC;
+        // columns of a chunk this slab does not have are parked beyond N, which disables them
+        cidx[u] = u < chunks ? n0 + (u * 32 + lane) * VEC : N;
 #pragma unroll
         for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
     }
@@ -95,14 +98,16 @@ __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ val
     }
 }
 
-// Columns covered by one warp for a given vector width and N: wide slabs for wide N so that the
-// staging of a row's indices is amortised over more B traffic.
+// Column chunks (of 32*vec columns) per warp slab: 1, 2 or 4.  Wider slabs amortise the staging of a
+// row's indices over more B traffic; beyond 4 chunks the accumulators push the kernel past 64
+// registers and the lost occupancy costs far more than the staging saves (measured: 8 chunks ran
+// 30 % slower).  A partly filled last slab costs little: its idle chunks issue no loads, and the
+// kernel is bound by L1 traffic, not by issue slots.  (Narrowing the slabs of a lone small matrix
+// to get more warps was tried and lost: 512 x 2048, N = 3136 went from 119 to 153 us.)
 __host__ __device__ inline int spmm_slab_chunks(int N, int vec)
 {
-    const int per = 32 * vec;
-    if (N > 4 * per) return 4;
-    if (N > per) return 2;
-    return 1;
+    const int total = (N + 32 * vec - 1) / (32 * vec);
+    return total > 4 ? 4 : total > 1 ? 2 : 1;
 }
 
 }  // namespace dlspm

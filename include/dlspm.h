@@ -42,7 +42,8 @@ typedef enum dlspm_status {
     DLSPM_ERR_CSR = 5,              /* CSR structure failed the sanity check             */
     DLSPM_ERR_NOMEM = 6,            /* host or device allocation failed                  */
     DLSPM_ERR_UNSUPPORTED = 7,      /* size beyond a documented limit                    */
-    DLSPM_ERR_NO_DEVICE = 8         /* no CUDA device / not an sm_100 device             */
+    DLSPM_ERR_NO_DEVICE = 8,        /* no CUDA device / not an sm_100 device             */
+    DLSPM_ERR_TIMEOUT = 9           /* a bounded wait inside a kernel ran out            */
 } dlspm_status;
 
 typedef struct dlspm_ctx dlspm_ctx;   /* one per device; not shared between host threads */
@@ -67,8 +68,15 @@ typedef enum dlspm_option {
      * reference CPU loop (SPMM/spmm-esimd-fromfile.cpp:63-83, built without FMA contraction)
      * bit for bit.  0 (default): fused multiply-add. */
     DLSPM_OPT_STRICT_FP32 = 0,
-    /* SpMM kernel choice: 0 = automatic, 1 = row-gather kernel, 2 = shared-memory tiled kernel. */
-    DLSPM_OPT_SPMM_KERNEL = 1
+    /* SpMM kernel choice in prepared batches and plans: 0 = automatic (cost model), 1 = row-gather
+     * kernel only, 2 = shared-memory tiled kernel wherever it applies (N % 4 == 0, aligned dense
+     * operands, strictly ascending columns in every row). */
+    DLSPM_OPT_SPMM_KERNEL = 1,
+    /* Threshold of the automatic choice, in thousandths: the tiled kernel is taken for problems
+     * whose fraction of nonzeros is at least value/1000.  Default 1001, i.e. never: on B200 the
+     * row-gather kernel is still the faster one at every density measured, so the tiled kernel runs
+     * only when asked for (this option or DLSPM_OPT_SPMM_KERNEL = 2). */
+    DLSPM_OPT_TILE_MIN_DENSITY = 2
 } dlspm_option;
 int dlspm_set_option(dlspm_ctx *ctx, int option, int value);
 int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value);
@@ -148,11 +156,23 @@ int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem
                                   void *stream);
 
 /* A prepared batch: the problem table and its tile index live on the device, so repeated
- * launches cost no host work. */
+ * launches cost no host work.  Creating it also analyses the patterns on the device: rows are
+ * ordered by length inside every problem (so that the warps of a tile finish together), and
+ * problems that are dense enough and have ascending columns are routed to the tiled kernel. */
 typedef struct dlspm_batch dlspm_batch;
 int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                        dlspm_batch **batch);
 int dlspm_batch_launch(dlspm_ctx *ctx, const dlspm_batch *batch, void *stream);
+/* Launches one part of a prepared batch only: 0 = everything (same as dlspm_batch_launch),
+ * 1 = the problems served by the row-gather kernel, 2 = those served by the tiled kernel.  Lets a
+ * benchmark time the two kernels separately. */
+int dlspm_batch_launch_part(dlspm_ctx *ctx, const dlspm_batch *batch, int part, void *stream);
+/* How many problems of the batch run on the row-gather and on the tiled kernel; (if device_error
+ * is not NULL: synchronises the device) whether a kernel of this batch gave up a bounded wait
+ * (0 = no); stats4 = {2*nnz*N, algorithmic bytes} of the row-gather part, then of the tiled part.
+ * Any pointer may be NULL. */
+int dlspm_batch_info(dlspm_ctx *ctx, const dlspm_batch *batch, int *gather_problems,
+                     int *tiled_problems, int *device_error, double *stats4);
 int dlspm_batch_destroy(dlspm_batch *batch);
 
 /* ---- host-buffer entry points (copies in and out included) ----------------------------- */

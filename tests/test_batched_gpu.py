@@ -215,3 +215,95 @@ def test_multi_device_layer(pkg, oracle):
 def test_fp32_peak_probe(ctx):
     t = ctx.measure_fp32_peak()
     assert 10.0 < t < 200.0, t
+
+
+def _run_prepared(pkg, ctx, dev, probs, kernel, min_density=None):
+    import torch
+
+    ctx.set_option(pkg.OPT_SPMM_KERNEL, kernel)
+    old_density = ctx.get_option(pkg.OPT_TILE_MIN_DENSITY)
+    if min_density is not None:
+        ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, min_density)
+    try:
+        arr = pkg.ProblemArray(len(probs))
+        outs = []
+        for i, (M, K, N, ro, ci, vals, B) in enumerate(probs):
+            Cd = torch.full((max(M * N, 1),), float("nan"), device=dev)[: M * N]
+            outs.append(Cd)
+            arr.set(i, M, K, N, int(ci.size), to_dev(vals, dev), to_dev(ro, dev), to_dev(ci, dev), to_dev(B, dev), Cd)
+        batch = ctx.batch_create(arr)
+        batch.launch()
+        batch.launch()
+        torch.cuda.synchronize()
+        info = batch.info(check_device=True)
+        batch.close()
+    finally:
+        ctx.set_option(pkg.OPT_SPMM_KERNEL, pkg.SPMM_KERNEL_AUTO)
+        ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, old_density)
+    return [o.cpu().numpy() for o in outs], info
+
+
+def tiled_cases(pkg):
+    """Shapes that exercise every edge of the 128 x 128 x 32 tiling."""
+    from cases import csr_from_lengths
+
+    cases = []
+    for (M, K, N, sp, seed) in [(128, 64, 128, 0.5, 1), (256, 256, 256, 0.5, 2), (130, 70, 132, 0.3, 3),
+                                (1, 33, 4, 0.5, 4), (64, 4096, 260, 0.7, 5), (300, 31, 1024, 0.2, 6),
+                                (512, 2048, 256, 0.5, 7), (257, 100, 3136, 0.6, 8)]:
+        ro, ci = csr_rowlen_normal(pkg, M, K, sp, 500 + seed)
+        cases.append((M, K, N, ro, ci, pkg.gen_dense_host(int(ci.size), 500 + seed, 2), dense(pkg, K, N, 500 + seed, 10)))
+    # empty rows, full rows, rows of exactly 32 and 33 entries
+    K, N = 96, 64
+    lengths = [0, 96, 32, 33, 1, 0, 95, 64, 0]
+    ro, ci = csr_from_lengths(pkg, K, lengths, seed=9)
+    cases.append((len(lengths), K, N, ro, ci, pkg.gen_dense_host(int(ci.size), 9, 2), dense(pkg, K, N, 9, 10)))
+    return cases
+
+
+def test_tiled_kernel_matches_gather_and_oracle(pkg, oracle, ctx, dev):
+    probs = tiled_cases(pkg)
+    tiled, info_t = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_TILED)
+    gather, info_g = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_GATHER)
+    assert info_t[1] == len(probs) and info_t[0] == 0 and info_t[2] == 0
+    assert info_g[0] == len(probs) and info_g[1] == 0
+    check_all(oracle, probs, tiled)
+    check_all(oracle, probs, gather)
+    # absent entries add fma(0, b, acc) = acc: the tiled kernel has the bits of the row-gather kernel
+    for a, b in zip(tiled, gather):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_tiled_kernel_strict_mode_is_bit_exact(pkg, oracle, ctx, dev):
+    probs = tiled_cases(pkg)[:4]
+    ctx.set_option(pkg.OPT_STRICT_FP32, 1)
+    try:
+        tiled, info = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_TILED)
+    finally:
+        ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+    assert info[1] == len(probs)
+    for (M, K, N, ro, ci, vals, B), out in zip(probs, tiled):
+        ref = oracle.spmm(vals, ro, ci, B, M, N)
+        assert np.array_equal(out.view(np.uint32), ref.ravel().view(np.uint32))
+
+
+def test_automatic_choice_and_ineligible_problems(pkg, oracle, ctx, dev):
+    """Unsorted rows, N % 4 != 0 and sparse patterns stay on the row-gather kernel; dense sorted
+    patterns go to the tiled kernel; results are right either way."""
+    from cases import shuffle_rows_columns
+
+    dense_sorted = tiled_cases(pkg)[1]                       # 256 x 256, half full
+    M, K, N, ro, ci, vals, B = tiled_cases(pkg)[6]
+    unsorted = (M, K, N, ro, shuffle_rows_columns(ro, ci, 3), vals, B)
+    ro2, ci2 = csr_rowlen_normal(pkg, 256, 256, 0.5, 77)
+    odd_n = (256, 256, 130, ro2, ci2, pkg.gen_dense_host(int(ci2.size), 77, 2), dense(pkg, 256, 130, 77, 10))
+    ro3, ci3 = csr_rowlen_normal(pkg, 512, 512, 0.98, 78)
+    sparse = (512, 512, 256, ro3, ci3, pkg.gen_dense_host(int(ci3.size), 78, 2), dense(pkg, 512, 256, 78, 10))
+    probs = [dense_sorted, unsorted, odd_n, sparse]
+    outs, info = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_AUTO, min_density=150)
+    assert info[0] == 3 and info[1] == 1 and info[2] == 0
+    check_all(oracle, probs, outs)
+    # forcing the tiled kernel still leaves the ineligible ones where they are
+    outs, info = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_TILED)
+    assert info[0] == 2 and info[1] == 2
+    check_all(oracle, probs, outs)
