@@ -415,6 +415,43 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
             sweep[f"{M}x{K}_n{N}"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 2.0 * nnz * N,
                                                 spmm_bytes(M, K, N, nnz), hbm_gbs, fp32_tflops)
     out["spmm_sweep_s0.9"] = sweep
+
+    # the same 15 cases at batch granularity: 24 independent copies of each (distinct seeds) in one
+    # prepared grouped launch, about 6 GB resident, so that launch latency and L2 residency drop out
+    import statistics as st
+
+    copies = 24
+    arr = pkg.ProblemArray(15 * copies)
+    keep, flops, nbytes, idx = [], 0.0, 0.0, 0
+    for (M, K) in SHAPES:
+        for N in WIDTHS:
+            for c in range(copies):
+                seed = 70000 + 100 * idx + c
+                ro = pkg.gen_rowlen_normal_host(M, K, 0.9, COV, seed)
+                nnz = int(ro[-1])
+                d_ro = up(ro)
+                d_ci = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)[:nnz]
+                ctx.gen_sample_columns(M, K, d_ro, seed, d_ci)
+                v = torch.empty(max(nnz, 1), device=dev)[:nnz]
+                ctx.gen_dense(v, seed, 2)
+                Bm = torch.empty(K * N, device=dev)
+                ctx.gen_dense(Bm, seed, 10)
+                Cm = torch.empty(M * N, device=dev)
+                arr.set(idx * copies + c, M, K, N, nnz, v, d_ro, d_ci, Bm, Cm)
+                flops += 2.0 * nnz * N
+                nbytes += spmm_bytes(M, K, N, nnz)
+            idx += 1
+    batch = ctx.batch_create(arr)
+    batch.launch()
+    torch.cuda.synchronize()
+    times = time_kernel(batch.launch, 5)
+    ms = st.median(times)
+    out["spmm_sweep_s0.9_batched"] = {
+        "problems": 15 * copies, "ms_median": ms, "gflops": flops / ms * 1e-6, "hbm_gbs": nbytes / ms * 1e-6,
+        "hbm_frac": nbytes / ms * 1e-6 / hbm_gbs,
+        "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / ms,
+        "binds": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (fp32_tflops * 1e12) else "fp32"}
+    batch.close()
     del flush
     return out
 

@@ -22,7 +22,11 @@ struct dlspm_ctx {
     size_t scratch_bytes;
     void *stage;  // staging for *_host entry points
     size_t stage_bytes;
-    cudaStream_t stream;  // private stream of the *_host entry points
+    cudaStream_t stream;  // private stream of the *_host entry points (compute)
+    // copy streams and events of the pipelined host-buffer batch (created on first use)
+    cudaStream_t h2d_stream, d2h_stream;
+    cudaEvent_t ev_h2d[2], ev_kernel[2], ev_d2h[2];
+    int pipeline_ready;
 };
 
 struct dlspm_plan {
@@ -54,6 +58,10 @@ static inline int dlspm_use(dlspm_ctx *ctx)
 // Grows ctx->scratch to at least `bytes` (contents are not preserved).
 int dlspm_scratch_reserve(dlspm_ctx *ctx, size_t bytes);
 int dlspm_stage_reserve(dlspm_ctx *ctx, size_t bytes);
+
+// One-shot grouped launch with caller-provided table memory (spmm.cu).
+size_t dlspm_batched_table_bytes(int count);
+int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st);
 
 static inline int dlspm_ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long dlspm_ceil_div64(long long a, long long b) { return (a + b - 1) / b; }

@@ -76,6 +76,15 @@ extern "C" int dlspm_destroy(dlspm_ctx *ctx)
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->pipeline_ready) {
+        cudaStreamDestroy(ctx->h2d_stream);
+        cudaStreamDestroy(ctx->d2h_stream);
+        for (int i = 0; i < 2; i++) {
+            cudaEventDestroy(ctx->ev_h2d[i]);
+            cudaEventDestroy(ctx->ev_kernel[i]);
+            cudaEventDestroy(ctx->ev_d2h[i]);
+        }
+    }
     (void)cudaGetLastError();
     delete ctx;
     return DLSPM_OK;

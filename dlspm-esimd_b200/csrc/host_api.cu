@@ -3,6 +3,7 @@
 // around their kernels (explicit memcpy before and after, SPMM/spmm-esimd-fromfile.cpp:172-180,255).
 // Device staging memory belongs to the context and is reused between calls.  Pinned host memory
 // makes the copies asynchronous DMA; pageable memory works too.
+#include <algorithm>
 #include <vector>
 
 #include "common.cuh"
@@ -128,39 +129,76 @@ extern "C" int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int
     return DLSPM_OK;
 }
 
-// Batched SpMM with host pointers.  The batch is cut into pieces whose device copies fit a staging
-// budget; each piece is copied in, run as one grouped launch, and its C blocks copied out.
+// Batched SpMM with host pointers, pipelined: the batch is cut into pieces of at most 256 MiB of
+// device copies; two staging buffers alternate, and three streams overlap the host-to-device copy
+// of piece i+1, the grouped launch of piece i and the device-to-host copy of piece i-1 (PCIe is
+// full duplex, so the slower of the two copy directions bounds the call, not their sum).
+namespace {
+
+int pipeline_init(dlspm_ctx *ctx)
+{
+    if (ctx->pipeline_ready) return DLSPM_OK;
+    DLSPM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+    DLSPM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+        DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_h2d[i], cudaEventDisableTiming));
+        DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_kernel[i], cudaEventDisableTiming));
+        DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_d2h[i], cudaEventDisableTiming));
+    }
+    ctx->pipeline_ready = 1;
+    return DLSPM_OK;
+}
+
+}  // namespace
+
 extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_problem *problems)
 {
     if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
-    const size_t budget = (size_t)4 << 30;
+    const size_t budget = (size_t)256 << 20;
     auto need = [](const dlspm_problem &q) {
         return padded(4 * ((size_t)q.M + 1)) + 2 * padded(4 * (size_t)q.nnz) + padded(4 * (size_t)q.K * q.N) +
                padded(4 * (size_t)q.M * q.N);
     };
+    size_t largest = 0;
     for (int i = 0; i < count; i++) {
         const dlspm_problem &q = problems[i];
         if (q.M < 0 || q.K < 0 || q.N < 0 || q.nnz < 0 || !q.row_offsets ||
             (q.nnz > 0 && (!q.values || !q.column_indices)) || ((size_t)q.K * q.N > 0 && !q.B) ||
             ((size_t)q.M * q.N > 0 && !q.C))
             return DLSPM_ERR_INVALID_ARGUMENT;
+        largest = std::max(largest, need(q));
     }
-    cudaStream_t st = ctx->stream;
-    std::vector<dlspm_problem> dev;
-    int first = 0;
-    while (first < count) {
+    if (count == 0) return DLSPM_OK;
+    rc = pipeline_init(ctx);
+    if (rc) return rc;
+    // pieces: consecutive problems up to the budget (a single larger problem is its own piece)
+    std::vector<int> piece_end;
+    size_t max_piece = 0, max_tables = 0;
+    for (int first = 0; first < count;) {
         size_t bytes = 0;
         int last = first;
-        while (last < count && (last == first || bytes + need(problems[last]) <= budget)) {
-            bytes += need(problems[last]);
-            last++;
-        }
-        rc = dlspm_stage_reserve(ctx, bytes + 256);
-        if (rc) return rc;
-        Carver cv(ctx->stage);
-        dev.clear();
+        while (last < count && (last == first || bytes + need(problems[last]) <= budget)) bytes += need(problems[last++]);
+        piece_end.push_back(last);
+        max_piece = std::max(max_piece, bytes);
+        max_tables = std::max(max_tables, dlspm_batched_table_bytes(last - first));
+        first = last;
+    }
+    const size_t slot = padded(max_piece) + padded(max_tables);
+    rc = dlspm_stage_reserve(ctx, 2 * slot + 256);
+    if (rc) return rc;
+    cudaStream_t h2d = ctx->h2d_stream, run = ctx->stream, d2h = ctx->d2h_stream;
+    std::vector<dlspm_problem> dev[2];
+    int first = 0;
+    for (size_t pi = 0; pi < piece_end.size(); pi++) {
+        const int last = piece_end[pi];
+        const int b = (int)(pi & 1);
+        char *base = (char *)ctx->stage + (size_t)b * slot;
+        // the slot is free once the results of the piece that used it two rounds ago have left
+        if (pi >= 2) DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(h2d, ctx->ev_d2h[b], 0));
+        Carver cv(base + padded(max_tables));
+        dev[b].clear();
         for (int i = first; i < last; i++) {
             const dlspm_problem &q = problems[i];
             dlspm_problem d = q;
@@ -169,28 +207,35 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
             float *d_v = cv.take<float>((size_t)q.nnz);
             float *d_B = cv.take<float>((size_t)q.K * q.N);
             float *d_C = cv.take<float>((size_t)q.M * q.N);
-            DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ro, q.row_offsets, 4 * ((size_t)q.M + 1), cudaMemcpyHostToDevice, st));
+            DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ro, q.row_offsets, 4 * ((size_t)q.M + 1), cudaMemcpyHostToDevice, h2d));
             if (q.nnz) {
-                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ci, q.column_indices, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, st));
-                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, q.values, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, st));
+                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ci, q.column_indices, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, h2d));
+                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, q.values, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, h2d));
             }
-            if ((size_t)q.K * q.N > 0) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_B, q.B, 4 * (size_t)q.K * q.N, cudaMemcpyHostToDevice, st));
+            if ((size_t)q.K * q.N > 0) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_B, q.B, 4 * (size_t)q.K * q.N, cudaMemcpyHostToDevice, h2d));
             d.row_offsets = d_ro;
             d.column_indices = d_ci;
             d.values = d_v;
             d.B = d_B;
             d.C = d_C;
-            dev.push_back(d);
+            dev[b].push_back(d);
         }
-        rc = dlspm_spmm_batched_f32(ctx, (int)dev.size(), dev.data(), st);
+        DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_h2d[b], h2d));
+        DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(run, ctx->ev_h2d[b], 0));
+        rc = dlspm_spmm_batched_at(ctx, (int)dev[b].size(), dev[b].data(), base, run);
         if (rc) return rc;
+        DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_kernel[b], run));
+        DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(d2h, ctx->ev_kernel[b], 0));
         for (int i = first; i < last; i++) {
             const dlspm_problem &q = problems[i];
             const size_t nC = (size_t)q.M * q.N;
-            if (nC) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(q.C, dev[(size_t)(i - first)].C, 4 * nC, cudaMemcpyDeviceToHost, st));
+            if (nC) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(q.C, dev[b][(size_t)(i - first)].C, 4 * nC, cudaMemcpyDeviceToHost, d2h));
         }
-        DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(st));
+        DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_d2h[b], d2h));
         first = last;
     }
+    DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(d2h));
+    DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(run));
+    DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(h2d));
     return DLSPM_OK;
 }

@@ -41,8 +41,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const Spmm
     const int row = a.row_order ? a.row_order[slot] : slot;
     const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
     spmm_warp_row_slab<VEC, U, STRICT>(a.values, a.cols, start, end, a.B,
-                                       a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * a.chunks,
-                                       a.chunks, lane, stage[warp]);
+                                       a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * U, lane,
+                                       stage[warp]);
 }
 
 template <int VEC, int U>
@@ -269,11 +269,11 @@ __device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, in
     float *Crow = p.C + (size_t)row * (size_t)p.N;
     const int n0 = slab * 32 * VEC * p.chunks;
     if (p.chunks == 4)
-        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
+        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
     else if (p.chunks == 2)
-        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
+        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
     else
-        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, p.chunks, lane, stage);
+        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
 }
 
 // Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
@@ -654,32 +654,47 @@ extern "C" int dlspm_batch_destroy(dlspm_batch *b)
     return DLSPM_OK;
 }
 
+// Bytes of device memory the tables of a one-shot grouped launch of `count` problems need.
+size_t dlspm_batched_table_bytes(int count)
+{
+    const size_t tab = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
+    const size_t st = (sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255;
+    return tab + st + 256;
+}
+
+// One-shot grouped launch with its tables placed at `tables` (device memory of at least
+// dlspm_batched_table_bytes(count) bytes, owned by the caller until the launch has finished).
+int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st)
+{
+    std::vector<BatchProblem> tab;
+    std::vector<long long> starts;
+    int rc = build_tables(count, problems, tab, starts);
+    if (rc) return rc;
+    if (tab.empty()) return DLSPM_OK;
+    const size_t tab_bytes = sizeof(BatchProblem) * tab.size();
+    const size_t st_off = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
+    const size_t st_bytes = sizeof(long long) * starts.size();
+    const size_t cnt_off = st_off + ((sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255);
+    char *base = (char *)tables;
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, tab.data(), tab_bytes, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, starts.data(), st_bytes, cudaMemcpyHostToDevice, st));
+    return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
+                               (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
+}
+
 // One-shot grouped launch: tables go to the context's scratch (no allocation once it is large
-// enough); the copy is stream-ordered, so the host vectors are pinned down by a synchronize-free
-// staging through cudaMemcpyAsync from pageable memory, which returns after the source is read.
+// enough).  The table copies are stream-ordered cudaMemcpyAsync calls from pageable memory, which
+// return once the source has been read, so the host vectors may go out of scope.
 extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                                       void *stream)
 {
     if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
-    std::vector<BatchProblem> tab;
-    std::vector<long long> starts;
-    rc = build_tables(count, problems, tab, starts);
+    if (count == 0) return DLSPM_OK;
+    rc = dlspm_scratch_reserve(ctx, dlspm_batched_table_bytes(count));
     if (rc) return rc;
-    if (tab.empty()) return DLSPM_OK;
-    const size_t tab_bytes = sizeof(BatchProblem) * tab.size();
-    const size_t st_off = (tab_bytes + 255) & ~(size_t)255;
-    const size_t st_bytes = sizeof(long long) * starts.size();
-    const size_t cnt_off = (st_off + st_bytes + 255) & ~(size_t)255;
-    rc = dlspm_scratch_reserve(ctx, cnt_off + 256);
-    if (rc) return rc;
-    char *base = (char *)ctx->scratch;
-    cudaStream_t st = (cudaStream_t)stream;
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, tab.data(), tab_bytes, cudaMemcpyHostToDevice, st));
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, starts.data(), st_bytes, cudaMemcpyHostToDevice, st));
-    return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
-                               (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
+    return dlspm_spmm_batched_at(ctx, count, problems, ctx->scratch, (cudaStream_t)stream);
 }
 
 // ---- grouped launch without any allocation ------------------------------------------------------

@@ -49,21 +49,18 @@ __device__ __forceinline__ float mad(float a, float b, float c)
     else return fmaf(a, b, c);
 }
 
-// stage: 32 int2 slots private to this warp.  U is the compiled number of column chunks per lane;
-// `chunks` (<= U) is how many of them this slab really has, so that the slab width can be any
-// multiple of 32*VEC up to 32*VEC*U (3136 columns are 5 slabs of 5 chunks, not 7 slabs of 4).
+// stage: 32 int2 slots private to this warp.
 template <int VEC, int U, bool STRICT>
 __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
                                                    const int *__restrict__ cols, int start, int end,
                                                    const float *__restrict__ B, float *__restrict__ Crow,
-                                                   int N, int n0, int chunks, int lane, int2 *stage)
+                                                   int N, int n0, int lane, int2 *stage)
 {
     float acc[U][VEC];
     int cidx[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
-        // columns of a chunk this slab does not have are parked beyond N, which disables them
-        cidx[u] = u < chunks ? n0 + (u * 32 + lane) * VEC : N;
+        cidx[u] = n0 + (u * 32 + lane) * VEC;
 #pragma unroll
         for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
     }
