@@ -39,6 +39,11 @@ WIDTHS = [256, 1024, 3136]
 COV = 0.4
 STREAM_PICK = 50
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per algorithmic byte of spmm_batched_kernel, from one ncu capture of a 256-problem
+# batch (dram__bytes_read.sum + dram__bytes_write.sum = 4.39 GB for 3.87 GB algorithmic; see
+# profiles/spmm_batched_kernel_256problems.md).  Traffic grows with the bytes of the problems
+# processed, so the ratio is applied to the full launch.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"spmm_batched_kernel": 1.134}
 
 
 def log(*a):
@@ -669,7 +674,10 @@ def main():
             "data": "synthetic", "config": workload_config(args, world),
             "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
-                         "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"of {peak_kind}",
+                         "frac": achieved / hbm_gbs,
+                         "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE[dominant] * dom["algorithmic_bytes_per_launch"]
+                                     if dominant in NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None),
+                         "peak_source": f"of {peak_kind}",
                          "kernel": dominant, "launch_ms": launch_avg_ms,
                          "algorithmic_bytes_per_launch": dom["algorithmic_bytes_per_launch"],
                          "fp32_peak_tflops_measured": fp32_tflops,

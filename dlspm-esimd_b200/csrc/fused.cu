@@ -37,9 +37,12 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    // column indices of the next pass are fetched one pass ahead
+    int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
     for (int base = start; base < end; base += 32) {
         const int p = base + lane;
-        const int col = p < end ? __ldg(cols + p) : -1;
+        const int col = col_next;
+        col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
         const float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
 #pragma unroll
         for (int k = 0; k < G; k++) {

@@ -30,9 +30,13 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     float4 a[R];
     load_row_chunks<G, R>(lhs4, chunks, t, a);
     const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    // the column indices of the next pass are fetched before this pass is computed, so that their
+    // latency does not sit in front of the rhs gathers of every pass
+    int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
     for (int base = start; base < end; base += 32) {
         const int p = base + lane;
-        const int col = p < end ? __ldg(cols + p) : -1;
+        const int col = col_next;
+        col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
         const float r = sddmm_pass<G, R>(a, rhs4, chunks, col, g, t);
         if (p < end) out[p] = r;
     }
