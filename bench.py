@@ -517,11 +517,55 @@ def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
     flops = 2.0 * total_nnz * N
     nbytes = spmm_bytes(M, K, N, total_nnz)
     ms = statistics.median(times)
-    return {"workload": "65536x65536 density 0.01 N=512, rows sharded by nnz, B replicated, C all-gathered",
-            "ms_total_median": ms, "ms_kernel_median": statistics.median(ktimes), "gflops": flops / ms * 1e-6,
-            "hbm_frac": nbytes / ms * 1e-6 / hbm_gbs,
-            "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / ms,
-            "nnz": total_nnz, "n_gpus": world}
+    out = {"workload": "65536x65536 density 0.01 N=512, rows sharded by nnz, B replicated, C blocks gathered on every GPU",
+           "nccl_gather": {"ms_total_median": ms, "ms_kernel_median": statistics.median(ktimes),
+                           "gflops": flops / ms * 1e-6},
+           "nnz": total_nnz, "n_gpus": world}
+    best_ms = ms
+    if world > 1:
+        # fused form: the SpMM epilogue stores every row into the full C of all ranks over NVLink
+        # (peer mappings through CUDA IPC), so no collective follows the kernel
+        full_ptr, handle = ctx.peer_alloc(M * N * 4)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        peers = [ctx.peer_open(h) for r, h in enumerate(handles) if r != rank]
+        dsts = [full_ptr] + peers
+        gathered = step()
+        for _ in range(2):
+            ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dsts, r0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ftimes = []
+        for _ in range(reps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dsts, r0)
+            e1.record()
+            e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ftimes.append(float(t[0]))
+        dist.barrier()
+        mine = pkg.DeviceArray(full_ptr, (M, N)).tensor(dev)
+        same = torch.tensor([1 if torch.equal(mine, gathered) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        fms = statistics.median(ftimes)
+        out["fused_peer_stores"] = {"ms_total_median": fms, "gflops": flops / fms * 1e-6,
+                                    "equals_nccl_result_on_every_rank": bool(int(same[0]))}
+        best_ms = min(best_ms, fms)
+        del mine, gathered
+        torch.cuda.synchronize()
+        dist.barrier()
+        for p in peers:
+            ctx.peer_close(p)
+        dist.barrier()
+        ctx.peer_free(full_ptr)
+    out.update({"ms_total_median": best_ms, "gflops": flops / best_ms * 1e-6,
+                "hbm_frac": nbytes / best_ms * 1e-6 / hbm_gbs,
+                "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / best_ms})
+    return out
 
 
 # ---- main arm ------------------------------------------------------------------------------------------------------

@@ -97,6 +97,12 @@ _SIGNATURES = {
     "dlspm_mg_spmm_batched_f32_host": (_I, [_P, _I, C.POINTER(Problem)]),
     "dlspm_mg_spmm_rowshard_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "dlspm_measure_fp32_peak": (_I, [_P, C.POINTER(C.c_double)]),
+    "dlspm_spmm_csr_f32_scatter": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _I, C.POINTER(_P), C.c_longlong, _P]),
+    "dlspm_enable_peer_access": (_I, [_P, _I]),
+    "dlspm_peer_alloc": (_I, [_P, C.c_size_t, C.POINTER(_P), C.c_char_p]),
+    "dlspm_peer_open": (_I, [_P, C.c_char_p, C.POINTER(_P)]),
+    "dlspm_peer_close": (_I, [_P, _P]),
+    "dlspm_peer_free": (_I, [_P, _P]),
 }
 
 
@@ -340,10 +346,56 @@ class Context:
             _dev_ptr(column_indices, torch.int32, "column_indices"), _stream_ptr(stream)),
             "dlspm_gen_bernoulli_fill", self)
 
+    # fused SpMM + gather over peer memory
+    def spmm_scatter(self, M, K, N, nnz, values, row_offsets, column_indices, B, dst_ptrs, first_row, stream=None):
+        """dst_ptrs: integer device addresses of the full-size C buffers (local first, then peers)."""
+        import torch
+
+        arr = (_P * len(dst_ptrs))(*dst_ptrs)
+        _check(self.lib.dlspm_spmm_csr_f32_scatter(
+            self.handle, M, K, N, nnz, _dev_ptr(values, torch.float32, "values"),
+            _dev_ptr(row_offsets, torch.int32, "row_offsets"), _dev_ptr(column_indices, torch.int32, "column_indices"),
+            _dev_ptr(B, torch.float32, "B"), len(dst_ptrs), arr, first_row, _stream_ptr(stream)),
+            "dlspm_spmm_csr_f32_scatter", self)
+
+    def enable_peer_access(self, peer_device: int) -> None:
+        _check(self.lib.dlspm_enable_peer_access(self.handle, peer_device), "dlspm_enable_peer_access", self)
+
+    def peer_alloc(self, nbytes: int):
+        """Returns (device address, 64-byte IPC handle)."""
+        ptr = _P()
+        handle = C.create_string_buffer(64)
+        _check(self.lib.dlspm_peer_alloc(self.handle, nbytes, C.byref(ptr), handle), "dlspm_peer_alloc", self)
+        return ptr.value, handle.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        ptr = _P()
+        _check(self.lib.dlspm_peer_open(self.handle, handle, C.byref(ptr)), "dlspm_peer_open", self)
+        return ptr.value
+
+    def peer_close(self, ptr: int) -> None:
+        _check(self.lib.dlspm_peer_close(self.handle, ptr), "dlspm_peer_close", self)
+
+    def peer_free(self, ptr: int) -> None:
+        _check(self.lib.dlspm_peer_free(self.handle, ptr), "dlspm_peer_free", self)
+
     def measure_fp32_peak(self) -> float:
         v = C.c_double()
         _check(self.lib.dlspm_measure_fp32_peak(self.handle, C.byref(v)), "dlspm_measure_fp32_peak", self)
         return v.value
+
+
+class DeviceArray:
+    """Zero-copy torch view of a raw device allocation (through __cuda_array_interface__)."""
+
+    def __init__(self, ptr: int, shape, typestr: str = "<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+    def tensor(self, device):
+        import torch
+
+        return torch.as_tensor(self, device=device)
 
 
 class Plan:

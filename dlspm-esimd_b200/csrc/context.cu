@@ -210,3 +210,73 @@ extern "C" int dlspm_measure_fp32_peak(dlspm_ctx *ctx, double *tflops)
     *tflops = flops / (best_ms * 1e-3) * 1e-12;
     return DLSPM_OK;
 }
+
+// ---- peer memory: buffers other GPUs (same or other process) can store into ---------------------
+extern "C" int dlspm_enable_peer_access(dlspm_ctx *ctx, int peer_device)
+{
+    if (!ctx || peer_device < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (peer_device == ctx->device) return DLSPM_OK;
+    int can = 0;
+    DLSPM_CUDA_TRY(ctx, cudaDeviceCanAccessPeer(&can, ctx->device, peer_device));
+    if (!can) return DLSPM_ERR_UNSUPPORTED;
+    cudaError_t err = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (err == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return DLSPM_OK;
+    }
+    if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaDeviceEnablePeerAccess");
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_peer_alloc(dlspm_ctx *ctx, size_t bytes, void **ptr, unsigned char handle[64])
+{
+    if (!ctx || !ptr || !handle || bytes == 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaError_t err = cudaMalloc(ptr, bytes);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "cudaMalloc(peer buffer)");
+        return DLSPM_ERR_NOMEM;
+    }
+    cudaIpcMemHandle_t h;
+    err = cudaIpcGetMemHandle(&h, *ptr);
+    if (err != cudaSuccess) {
+        cudaFree(*ptr);
+        *ptr = nullptr;
+        return dlspm_cuda_fail(ctx, err, "cudaIpcGetMemHandle");
+    }
+    memcpy(handle, &h, 64);
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_peer_open(dlspm_ctx *ctx, const unsigned char handle[64], void **ptr)
+{
+    if (!ctx || !ptr || !handle) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    DLSPM_CUDA_TRY(ctx, cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_peer_close(dlspm_ctx *ctx, void *ptr)
+{
+    if (!ctx || !ptr) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    DLSPM_CUDA_TRY(ctx, cudaIpcCloseMemHandle(ptr));
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_peer_free(dlspm_ctx *ctx, void *ptr)
+{
+    if (!ctx || !ptr) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    DLSPM_CUDA_TRY(ctx, cudaFree(ptr));
+    return DLSPM_OK;
+}

@@ -118,6 +118,129 @@ extern "C" int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan
                        (cudaStream_t)stream);
 }
 
+// ---- SpMM whose result rows go to several destinations (fused compute + gather) -----------------
+// A row-sharded SpMM needs its row block in the full C of every GPU afterwards.  Instead of running
+// the product and then a collective, the epilogue stores each finished row segment into every
+// destination buffer: the local C and the peers' C, reached through peer mappings (NVLink).  The
+// remote stores are fire-and-forget and overlap with the gathers of the rows still being computed.
+namespace {
+
+constexpr int kMaxDst = 8;
+
+struct ScatterArgs {
+    SpmmArgs a;
+    float *dst[kMaxDst];  // full-size C buffers (local and peers)
+    long long first_row;  // global row of local row 0
+    int ndst;
+};
+
+template <int VEC, int U>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(const ScatterArgs s)
+{
+    __shared__ int2 stage[kWarpsPerCta][32];
+    const SpmmArgs &a = s.a;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long tile = blockIdx.x;
+    const int slab = (int)(tile / a.row_groups);
+    const int rg = (int)(tile - (long long)slab * a.row_groups);
+    const int slot = rg * kWarpsPerCta + warp;
+    if (slot >= a.M) return;
+    const int row = a.row_order ? a.row_order[slot] : slot;
+    const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
+    const int n0 = slab * 32 * VEC * U;
+    // accumulate exactly as spmm_warp_row_slab does, then store the slab to every destination
+    float acc[U][VEC];
+    int cidx[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        cidx[u] = n0 + (u * 32 + lane) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
+    }
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        int2 cv = make_int2(0, 0);
+        if (p < end) cv = make_int2(__ldg(a.cols + p), __float_as_int(__ldg(a.values + p)));
+        stage[warp][lane] = cv;
+        __syncwarp();
+        const int cnt = min(32, end - base);
+#pragma unroll 4
+        for (int j = 0; j < cnt; j++) {
+            const int2 e = stage[warp][j];
+            const float av = __int_as_float(e.y);
+            const float *brow = a.B + (size_t)e.x * (size_t)a.N;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (cidx[u] < a.N) {
+                    float b[VEC];
+                    load_vec<VEC>(brow + cidx[u], b);
+#pragma unroll
+                    for (int v = 0; v < VEC; v++) acc[u][v] = fmaf(av, b[v], acc[u][v]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    const size_t off = (size_t)(s.first_row + row) * (size_t)a.N;
+    for (int d = 0; d < s.ndst; d++) {
+        float *crow = s.dst[d] + off;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (cidx[u] < a.N) store_vec<VEC>(crow + cidx[u], acc[u]);
+    }
+}
+
+template <int VEC, int U>
+void launch_scatter(const ScatterArgs &s, cudaStream_t st)
+{
+    const int slabs = dlspm_ceil_div(s.a.N, 32 * VEC * U);
+    spmm_rows_scatter_kernel<VEC, U><<<(unsigned)((long long)s.a.row_groups * slabs), kWarpsPerCta * 32, 0, st>>>(s);
+}
+
+}  // namespace
+
+extern "C" int dlspm_spmm_csr_f32_scatter(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                                          const int *row_offsets, const int *column_indices, const float *B,
+                                          int ndst, float *const *C_dsts, long long first_row, void *stream)
+{
+    if (!ctx || ndst < 1 || ndst > kMaxDst || !C_dsts || first_row < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = check_spmm_args(M, K, N, nnz, values, row_offsets, column_indices, B, C_dsts[0]);
+    if (rc) return rc;
+    rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return DLSPM_OK;
+    ScatterArgs s;
+    s.a = SpmmArgs{values, row_offsets, column_indices, B, nullptr, nullptr, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1};
+    s.first_row = first_row;
+    s.ndst = ndst;
+    const void *align_probe = B;
+    for (int d = 0; d < kMaxDst; d++) {
+        s.dst[d] = d < ndst ? C_dsts[d] : nullptr;
+        if (d < ndst) {
+            if (!C_dsts[d]) return DLSPM_ERR_INVALID_ARGUMENT;
+            if (((uintptr_t)C_dsts[d] % 16) != 0) align_probe = C_dsts[d];  // forces the narrow path
+        }
+    }
+    const int vec = dlspm_vec_width(N, B, align_probe);
+    const int U = spmm_slab_chunks(N, vec);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (vec == 4) {
+        if (U == 4) launch_scatter<4, 4>(s, st);
+        else if (U == 2) launch_scatter<4, 2>(s, st);
+        else launch_scatter<4, 1>(s, st);
+    } else if (vec == 2) {
+        if (U == 4) launch_scatter<2, 4>(s, st);
+        else if (U == 2) launch_scatter<2, 2>(s, st);
+        else launch_scatter<2, 1>(s, st);
+    } else {
+        if (U == 4) launch_scatter<1, 4>(s, st);
+        else if (U == 2) launch_scatter<1, 2>(s, st);
+        else launch_scatter<1, 1>(s, st);
+    }
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
 // ---- plan: rows binned by length --------------------------------------------------------------
 namespace {
 

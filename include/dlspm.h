@@ -277,6 +277,28 @@ int dlspm_mg_spmm_rowshard_f32_host(dlspm_mg *mg, int M, int K, int N, int nnz,
                                     const float *values, const int *row_offsets,
                                     const int *column_indices, const float *B, float *C);
 
+/* ---- fused SpMM + gather over peer memory ------------------------------------------------------- */
+
+/* Row-sharded SpMM whose epilogue is the gather: computes the M local rows (global rows first_row ..
+ * first_row+M-1) and stores each of them into all `ndst` (<= 8) destination matrices C_dsts[d]
+ * (full-size row-major C buffers: the local one and the peers', reached through peer mappings), so
+ * no collective follows.  C_dsts is a HOST array of device pointers.  After every participating GPU
+ * has finished its launch (stream synchronise + a host-side barrier between the processes or
+ * threads), every destination holds the complete C.  The reference has no multi-GPU path
+ * (SPMM/batch-run-spmm_fromfile:45 pins one device). */
+int dlspm_spmm_csr_f32_scatter(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                               const int *row_offsets, const int *column_indices, const float *B,
+                               int ndst, float *const *C_dsts, long long first_row, void *stream);
+/* Same process, several devices: lets kernels of this context's device store into memory of
+ * peer_device (cudaDeviceEnablePeerAccess). */
+int dlspm_enable_peer_access(dlspm_ctx *ctx, int peer_device);
+/* Other processes: allocate a device buffer and get the 64-byte handle a peer process turns into a
+ * pointer with dlspm_peer_open (CUDA IPC); close / free when done. */
+int dlspm_peer_alloc(dlspm_ctx *ctx, size_t bytes, void **ptr, unsigned char handle[64]);
+int dlspm_peer_open(dlspm_ctx *ctx, const unsigned char handle[64], void **ptr);
+int dlspm_peer_close(dlspm_ctx *ctx, void *ptr);
+int dlspm_peer_free(dlspm_ctx *ctx, void *ptr);
+
 /* ---- measurement helpers ------------------------------------------------------------------ */
 
 /* Sustained fp32 FMA rate of the device in TFLOP/s (a register-only FMA loop over all SMs); the
