@@ -562,9 +562,10 @@ def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
             ctx.peer_close(p)
         dist.barrier()
         ctx.peer_free(full_ptr)
+    # roofs of `world` GPUs together (B is read by every GPU: algorithmic bytes count it once)
     out.update({"ms_total_median": best_ms, "gflops": flops / best_ms * 1e-6,
-                "hbm_frac": nbytes / best_ms * 1e-6 / hbm_gbs,
-                "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / best_ms})
+                "hbm_frac": nbytes / best_ms * 1e-6 / (hbm_gbs * world),
+                "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / best_ms / world})
     return out
 
 
