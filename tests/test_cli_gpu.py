@@ -1,0 +1,78 @@
+"""The command-line drivers (the reference's `./app <file>.smtx <N>` programs): report lines, CSV
+columns and the printed CPU-vs-GPU difference."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(pkg, name, *args):
+    exe = os.path.join(pkg.PKG_DIR, "bin", name)
+    assert os.path.exists(exe), f"{exe} not built"
+    p = subprocess.run([exe, *map(str, args)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout
+    return p.stdout
+
+
+def _value(text, pattern):
+    m = re.search(pattern, text)
+    assert m, f"{pattern!r} not found in:\n{text}"
+    return float(m.group(1))
+
+
+def test_spmm_fromfile(pkg, tmp_path):
+    ro, ci = pkg.gen_bernoulli_csr_host(300, 200, 0.1, 5)
+    smtx = str(tmp_path / "a.smtx")
+    csv = str(tmp_path / "out.csv")
+    pkg.write_smtx(smtx, 300, 200, ro, ci)
+    out = _run(pkg, "spmm-fromfile", smtx, 64, "--csv", csv)
+    assert f"MSZ: 300, KSZ: 200, NSZ: 64, nnz: {ci.size}" in out
+    assert "Total kernel time was" in out and "GFLOPS:" in out
+    # inputs in [0,1): outputs of order nnz/row * 0.25, differences at rounding level
+    assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+    cpu, gpu = _value(out, r"checksum_cpu = ([0-9.e+-]+)"), _value(out, r"checksum_gpu = ([0-9.e+-]+)")
+    assert abs(cpu - gpu) <= 1e-5 * cpu
+    row = open(csv).read().strip().split(",")
+    assert len(row) == 7 and [int(row[0]), int(row[1]), int(row[2])] == [300, 64, 200]  # M,N,K,density,gflops,max_diff,opcount
+    # planned and signed variants give a report as well
+    out = _run(pkg, "spmm-fromfile", smtx, 100, "--planned", "--signed", "--cold")
+    assert "cold-L2 median ms" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+
+
+def test_spmm_fromfile_errors(pkg, tmp_path):
+    out = _run(pkg, "spmm-fromfile")
+    assert "Usage: ./app <filename>.smtx <batchsize>" in out
+    exe = os.path.join(pkg.PKG_DIR, "bin", "spmm-fromfile")
+    p = subprocess.run([exe, str(tmp_path / "missing.smtx"), "16"], stdout=subprocess.PIPE, text=True)
+    assert "Error opening file!" in p.stdout
+    bad = tmp_path / "bad.smtx"
+    bad.write_text("2, 2, 2\n0 1 2\n0 5\n")
+    p = subprocess.run([exe, str(bad), "16"], stdout=subprocess.PIPE, text=True)
+    assert "a_column_indices[i] >= KSZ" in p.stdout
+
+
+def test_sddmm_fromfile_and_fused(pkg, tmp_path):
+    ro, ci = pkg.gen_bernoulli_csr_host(256, 128, 0.2, 6)
+    smtx = str(tmp_path / "b.smtx")
+    csv = str(tmp_path / "s.csv")
+    pkg.write_smtx(smtx, 256, 128, ro, ci)
+    out = _run(pkg, "sddmm-fromfile", smtx, 128, "--csv", csv)
+    assert "GFLOPS :" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-3
+    row = open(csv).read().strip().split(",")
+    assert len(row) == 7 and [int(row[0]), int(row[1]), int(row[2])] == [256, 128, 128]  # M,K,N,density,gflops,flops,max_diff
+    out = _run(pkg, "fused", 512, 512, 32, 0.1)
+    assert "GFLOPS/s :" in out and "checksum_e using gpu" in out
+    assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
+    out = _run(pkg, "fused", 256, 256, 64, 0.05, "--band", 8)
+    assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
+
+
+def test_sweep_drivers_single_case(pkg):
+    out = _run(pkg, "spmm-allbenchs", 1024, 1024, 32, 0.1)
+    assert "GFLOPS:" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+    out = _run(pkg, "sddmm-allbench", 1024, 1024, 32, 0.1)
+    assert "GFLOPS :" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
