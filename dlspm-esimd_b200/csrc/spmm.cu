@@ -45,6 +45,87 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const Spmm
                                        stage[warp]);
 }
 
+// Few long rows: the S warps of a group share one row, each taking every S-th run of 32 nonzeros;
+// the partial slabs are added in a fixed order through shared memory, so the result is deterministic
+// (but not in CSR order: this path is not used in strict mode).  8/S rows per thread block.
+template <int VEC, int U, int S>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_split_kernel(const SpmmArgs a)
+{
+    __shared__ int2 stage[kWarpsPerCta][32];
+    __shared__ float part[kWarpsPerCta][U][32 * VEC];
+    constexpr int kRows = kWarpsPerCta / S;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = warp % S, local = warp / S;
+    const long long tile = blockIdx.x;
+    const int slab = (int)(tile / a.row_groups);
+    const int rg = (int)(tile - (long long)slab * a.row_groups);
+    const int slot = rg * kRows + local;
+    const bool active = slot < a.M;
+    const int row = active ? (a.row_order ? a.row_order[slot] : slot) : 0;
+    const int n0 = slab * 32 * VEC * U;
+    float acc[U][VEC];
+    int cidx[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        cidx[u] = n0 + (u * 32 + lane) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
+    }
+    if (active) {
+        const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
+        for (int base = start + 32 * split; base < end; base += 32 * S) {
+            const int p = base + lane;
+            int2 cv = make_int2(0, 0);
+            if (p < end) cv = make_int2(__ldg(a.cols + p), __float_as_int(__ldg(a.values + p)));
+            stage[warp][lane] = cv;
+            __syncwarp();
+            const int cnt = min(32, end - base);
+#pragma unroll 4
+            for (int j = 0; j < cnt; j++) {
+                const int2 e = stage[warp][j];
+                const float av = __int_as_float(e.y);
+                const float *brow = a.B + (size_t)e.x * (size_t)a.N;
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if (cidx[u] < a.N) {
+                        float b[VEC];
+                        load_vec<VEC>(brow + cidx[u], b);
+#pragma unroll
+                        for (int v = 0; v < VEC; v++) acc[u][v] = fmaf(av, b[v], acc[u][v]);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    }
+    if (split != 0) {
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int v = 0; v < VEC; v++) part[warp][u][lane * VEC + v] = acc[u][v];
+    }
+    __syncthreads();
+    if (split == 0 && active) {
+#pragma unroll
+        for (int sidx = 1; sidx < S; sidx++)
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int v = 0; v < VEC; v++) acc[u][v] += part[warp + sidx][u][lane * VEC + v];
+        float *crow = a.C + (size_t)row * (size_t)a.N;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (cidx[u] < a.N) store_vec<VEC>(crow + cidx[u], acc[u]);
+    }
+}
+
+template <int VEC, int U, int S>
+void launch_rows_split(SpmmArgs a, int slabs, cudaStream_t st)
+{
+    a.row_groups = dlspm_ceil_div(a.M, kWarpsPerCta / S);
+    spmm_rows_split_kernel<VEC, U, S><<<(unsigned)((long long)a.row_groups * slabs), kWarpsPerCta * 32, 0, st>>>(a);
+}
+
 template <int VEC, int U>
 void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
 {
@@ -54,15 +135,40 @@ void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
     else spmm_rows_kernel<VEC, U, false><<<grid, block, 0, st>>>(a);
 }
 
+template <int VEC, int U>
+void launch_rows_maybe_split(const SpmmArgs &a, int slabs, int split, bool strict, cudaStream_t st)
+{
+    if (split == 8) launch_rows_split<VEC, U, 8>(a, slabs, st);
+    else if (split == 4) launch_rows_split<VEC, U, 4>(a, slabs, st);
+    else if (split == 2) launch_rows_split<VEC, U, 2>(a, slabs, st);
+    else launch_rows<VEC, U>(a, slabs, strict, st);
+}
+
+// `split`: warps per row (1, 2, 4 or 8), see spmm_row_split.
 template <int VEC>
-void launch_rows_vec(SpmmArgs a, bool strict, cudaStream_t st)
+void launch_rows_vec(SpmmArgs a, int split, bool strict, cudaStream_t st)
 {
     a.chunks = spmm_slab_chunks(a.N, VEC);
     const int slabs = dlspm_ceil_div(a.N, 32 * VEC * a.chunks);
     const int U = a.chunks;
-    if (U == 4) launch_rows<VEC, 4>(a, slabs, strict, st);
-    else if (U == 2) launch_rows<VEC, 2>(a, slabs, strict, st);
-    else launch_rows<VEC, 1>(a, slabs, strict, st);
+    if (U == 4) launch_rows_maybe_split<VEC, 4>(a, slabs, split, strict, st);
+    else if (U == 2) launch_rows_maybe_split<VEC, 2>(a, slabs, split, strict, st);
+    else launch_rows_maybe_split<VEC, 1>(a, slabs, split, strict, st);
+}
+
+// Warps per row for a lone matrix: with few rows one warp per (row, slab) leaves most of the device
+// idle, so long rows are shared by 2, 4 or 8 warps until about 32 warps per SM exist or a warp would
+// get fewer than 64 nonzeros.
+int spmm_row_split(const dlspm_ctx *ctx, int M, int N, int nnz, int vec, bool strict)
+{
+    if (strict || M <= 0) return 1;
+    const int chunks = spmm_slab_chunks(N, vec);
+    const long long warps = (long long)M * dlspm_ceil_div(N, 32 * vec * chunks);
+    const long long want = (long long)ctx->sm_count * 32;
+    const double avg = (double)nnz / (double)M;
+    int s = 1;
+    while (s < 8 && warps * s < want && avg / (2 * s) >= 64.0) s *= 2;
+    return s;
 }
 
 int check_spmm_args(int M, int K, int N, int nnz, const float *values, const int *row_offsets,
@@ -75,16 +181,17 @@ int check_spmm_args(int M, int K, int N, int nnz, const float *values, const int
     return DLSPM_OK;
 }
 
-int spmm_launch(dlspm_ctx *ctx, int M, int N, const float *values, const int *row_offsets,
+int spmm_launch(dlspm_ctx *ctx, int M, int N, int nnz, const float *values, const int *row_offsets,
                 const int *cols, const float *B, float *C, const int *row_order, cudaStream_t st)
 {
     if (M == 0 || N == 0) return DLSPM_OK;
     SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1};
     const int vec = dlspm_vec_width(N, B, C);
     const bool strict = ctx->strict_fp32 != 0;
-    if (vec == 4) launch_rows_vec<4>(a, strict, st);
-    else if (vec == 2) launch_rows_vec<2>(a, strict, st);
-    else launch_rows_vec<1>(a, strict, st);
+    const int split = spmm_row_split(ctx, M, N, nnz, vec, strict);
+    if (vec == 4) launch_rows_vec<4>(a, split, strict, st);
+    else if (vec == 2) launch_rows_vec<2>(a, split, strict, st);
+    else launch_rows_vec<1>(a, split, strict, st);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
@@ -100,7 +207,7 @@ extern "C" int dlspm_spmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, 
     if (rc) return rc;
     rc = dlspm_use(ctx);
     if (rc) return rc;
-    return spmm_launch(ctx, M, N, values, row_offsets, column_indices, B, C, nullptr,
+    return spmm_launch(ctx, M, N, nnz, values, row_offsets, column_indices, B, C, nullptr,
                        (cudaStream_t)stream);
 }
 
@@ -114,7 +221,7 @@ extern "C" int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan
     if (rc) return rc;
     rc = dlspm_use(ctx);
     if (rc) return rc;
-    return spmm_launch(ctx, plan->M, N, values, row_offsets, column_indices, B, C, plan->row_order,
+    return spmm_launch(ctx, plan->M, N, plan->nnz, values, row_offsets, column_indices, B, C, plan->row_order,
                        (cudaStream_t)stream);
 }
 
