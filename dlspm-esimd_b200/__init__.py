@@ -97,6 +97,7 @@ _SIGNATURES = {
     "dlspm_mg_spmm_batched_f32_host": (_I, [_P, _I, C.POINTER(Problem)]),
     "dlspm_mg_spmm_rowshard_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "dlspm_measure_fp32_peak": (_I, [_P, C.POINTER(C.c_double)]),
+    "dlspm_selftest_bounded_wait": (_I, [_P, C.c_uint, C.POINTER(_I)]),
     "dlspm_spmm_csr_f32_scatter": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _I, C.POINTER(_P), C.c_longlong, _P]),
     "dlspm_enable_peer_access": (_I, [_P, _I]),
     "dlspm_peer_alloc": (_I, [_P, C.c_size_t, C.POINTER(_P), C.c_char_p]),
@@ -378,6 +379,12 @@ class Context:
 
     def peer_free(self, ptr: int) -> None:
         _check(self.lib.dlspm_peer_free(self.handle, ptr), "dlspm_peer_free", self)
+
+    def selftest_bounded_wait(self, polls: int = 1000):
+        """(status, timed_out) of the bounded-wait self-test; the context stays usable afterwards."""
+        t = _I()
+        st = self.lib.dlspm_selftest_bounded_wait(self.handle, polls, C.byref(t))
+        return st, t.value
 
     def measure_fp32_peak(self) -> float:
         v = C.c_double()

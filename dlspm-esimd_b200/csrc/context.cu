@@ -280,3 +280,39 @@ extern "C" int dlspm_peer_free(dlspm_ctx *ctx, void *ptr)
     DLSPM_CUDA_TRY(ctx, cudaFree(ptr));
     return DLSPM_OK;
 }
+
+// ---- bounded-wait self-test --------------------------------------------------------------------
+// Every wait inside a kernel of this library is a bounded poll that ends in a status, never a trap
+// or an endless loop.  This entry point shows that path without any fault: one thread polls an
+// mbarrier that nothing will ever complete, gives up after `polls` tries and reports it.
+__global__ void bounded_wait_selftest_kernel(unsigned polls, int *timed_out)
+{
+    __shared__ unsigned long long bar;
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    unsigned done = 0;
+    for (unsigned i = 0; i < polls && !done; i++) {
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr)
+            : "memory");
+    }
+    *timed_out = done ? 0 : 1;
+}
+
+extern "C" int dlspm_selftest_bounded_wait(dlspm_ctx *ctx, unsigned polls, int *timed_out)
+{
+    if (!ctx || !timed_out || polls == 0 || polls > (1u << 20)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    rc = dlspm_scratch_reserve(ctx, 256);
+    if (rc) return rc;
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->scratch, 0, sizeof(int), ctx->stream));
+    bounded_wait_selftest_kernel<<<1, 1, 0, ctx->stream>>>(polls, (int *)ctx->scratch);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(timed_out, ctx->scratch, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return *timed_out ? DLSPM_ERR_TIMEOUT : DLSPM_OK;
+}

@@ -299,6 +299,14 @@ int dlspm_peer_open(dlspm_ctx *ctx, const unsigned char handle[64], void **ptr);
 int dlspm_peer_close(dlspm_ctx *ctx, void *ptr);
 int dlspm_peer_free(dlspm_ctx *ctx, void *ptr);
 
+/* ---- failure reporting ---------------------------------------------------------------------------- */
+
+/* No kernel of the library waits without a limit: a wait that runs out sets a status word and the
+ * kernel returns (DLSPM_ERR_TIMEOUT through dlspm_batch_info).  This self-test exercises exactly that
+ * path with no fault involved: one thread polls, at most `polls` (<= 2^20) times, an mbarrier that
+ * nothing completes.  Returns DLSPM_ERR_TIMEOUT with *timed_out = 1, and the context stays usable. */
+int dlspm_selftest_bounded_wait(dlspm_ctx *ctx, unsigned polls, int *timed_out);
+
 /* ---- measurement helpers ------------------------------------------------------------------ */
 
 /* Sustained fp32 FMA rate of the device in TFLOP/s (a register-only FMA loop over all SMs); the

@@ -312,3 +312,19 @@ def test_automatic_choice_and_ineligible_problems(pkg, oracle, ctx, dev):
     outs, info = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_TILED)
     assert info[0] == 2 and info[1] == 2
     check_all(oracle, probs, outs)
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(pkg, oracle, ctx, dev):
+    """A wait that nothing satisfies ends in a status, not in a hang; kernels run normally afterwards."""
+    import torch
+
+    st, timed_out = ctx.selftest_bounded_wait(2000)
+    assert st == pkg.ERR_TIMEOUT and timed_out == 1
+    assert "bounded wait" in pkg.strerror(st)
+    M, K, N, ro, ci, vals, B = 64, 64, 32, *spmm_case(pkg, 64, 64, 32, 0.2, seed=3)
+    Cd = torch.empty(M, N, device=dev)
+    ctx.spmm(M, K, N, int(ci.size), to_dev(vals, dev), to_dev(ro, dev), to_dev(ci, dev), to_dev(B, dev), Cd)
+    torch.cuda.synchronize()
+    bad, worst = oracle.violations(oracle.spmm(vals, ro, ci, B, M, N), Cd.cpu().numpy(),
+                                   oracle.spmm_scale(vals, ro, ci, B, M, N), TOL)
+    assert bad == 0, worst
