@@ -40,9 +40,8 @@ COV = 0.4
 STREAM_PICK = 50
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per algorithmic byte of spmm_batched_kernel, from one ncu capture of a 256-problem
-# batch (dram__bytes_read.sum + dram__bytes_write.sum = 4.39 GB for 3.87 GB algorithmic; see
-# profiles/spmm_batched_kernel_256problems.md).  Traffic grows with the bytes of the problems
-# processed, so the ratio is applied to the full launch.
+# batch (dram__bytes_read.sum + dram__bytes_write.sum = 4.39 GB for 3.87 GB algorithmic).  Traffic
+# grows with the bytes of the problems processed, so the ratio is applied to the full launch.
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"spmm_batched_kernel": 1.134}
 
 
