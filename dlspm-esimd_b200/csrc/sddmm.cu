@@ -42,6 +42,41 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     }
 }
 
+// Inner dimension beyond 1024 (16-byte aligned rows): the lanes' partial dot products of a pass are
+// accumulated over segments of 32*R float4 and reduced once at the end of the pass; the lhs segment
+// is re-read from L1 for every pass, which adds 3 % to the rhs traffic.
+template <int R>
+__global__ void __launch_bounds__(kWarps * 32)
+sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                       const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
+                       int M, int chunks)
+{
+    constexpr int G = 32, kSeg = G * R;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const float4 *lhs4 = reinterpret_cast<const float4 *>(lhs) + (size_t)row * (size_t)chunks;
+    const float4 *rhs4 = reinterpret_cast<const float4 *>(rhs);
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
+    for (int base = start; base < end; base += 32) {
+        const int p = base + lane;
+        const int col = col_next;
+        col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
+        float part[G];
+#pragma unroll
+        for (int k = 0; k < G; k++) part[k] = 0.f;
+        for (int seg = 0; seg < chunks; seg += kSeg) {
+            const int len = min(kSeg, chunks - seg);
+            float4 a[R];
+            load_row_chunks<G, R>(lhs4 + seg, len, lane, a);
+            sddmm_accumulate<G, R>(part, a, rhs4 + seg, len, chunks, col, 0, lane);
+        }
+        group_transpose_reduce<G>(part, lane);
+        if (p < end) out[p] = part[0];
+    }
+}
+
 // Any N and alignment: each lane strides over the row; one full-warp reduction per nonzero.
 template <int VEC>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -121,7 +156,7 @@ extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
         else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
         else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
     } else if (vec == 4) {
-        sddmm_generic_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+        sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
     } else if (vec == 2) {
         sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
     } else {

@@ -52,17 +52,20 @@ __device__ __forceinline__ void load_row_chunks(const float4 *__restrict__ row4,
 
 // One pass of sampled dot products: col = this lane's column index of nonzero base+lane (or -1
 // past the end of the row).  On return part0 on lane g*G+t is dot(lhs_row, rhs[col of that lane]).
+// Adds to part[k] the partial dot product of this lane for the k-th nonzero of its group.  `chunks`
+// is the number of float4 of the row (or row segment) that take part, `stride4` the row stride of
+// rhs in float4 (they differ when a long row is processed in segments).
 template <int G, int R>
-__device__ __forceinline__ float sddmm_pass(const float4 (&a)[R], const float4 *__restrict__ rhs4,
-                                            int chunks, int col, int g, int t)
+__device__ __forceinline__ void sddmm_accumulate(float (&part)[G], const float4 (&a)[R],
+                                                 const float4 *__restrict__ rhs4, int chunks, int stride4,
+                                                 int col, int g, int t)
 {
-    float part[G];
 #pragma unroll
     for (int k = 0; k < G; k++) {
         const int c = __shfl_sync(0xffffffffu, col, g * G + k);
-        float acc = 0.f;
+        float acc = part[k];
         if (c >= 0) {
-            const float4 *brow = rhs4 + (size_t)c * (size_t)chunks;
+            const float4 *brow = rhs4 + (size_t)c * (size_t)stride4;
 #pragma unroll
             for (int r = 0; r < R; r++) {
                 const int idx = r * G + t;
@@ -71,6 +74,16 @@ __device__ __forceinline__ float sddmm_pass(const float4 (&a)[R], const float4 *
         }
         part[k] = acc;
     }
+}
+
+template <int G, int R>
+__device__ __forceinline__ float sddmm_pass(const float4 (&a)[R], const float4 *__restrict__ rhs4,
+                                            int chunks, int col, int g, int t)
+{
+    float part[G];
+#pragma unroll
+    for (int k = 0; k < G; k++) part[k] = 0.f;
+    sddmm_accumulate<G, R>(part, a, rhs4, chunks, chunks, col, g, t);
     group_transpose_reduce<G>(part, t);
     return part[0];
 }
