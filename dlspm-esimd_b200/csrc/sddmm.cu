@@ -156,7 +156,10 @@ extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
         else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
         else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
     } else if (vec == 4) {
-        sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
+        // measured: 512-float segments (80 registers, 3 blocks per SM) win from N = 3136, 1024-float
+        // segments below that
+        if (N > 2048) sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
+        else sddmm_rows_long_kernel<8><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
     } else if (vec == 2) {
         sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
     } else {
