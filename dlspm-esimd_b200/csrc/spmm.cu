@@ -126,6 +126,62 @@ void launch_rows_split(SpmmArgs a, int slabs, cudaStream_t st)
     spmm_rows_split_kernel<VEC, U, S><<<(unsigned)((long long)a.row_groups * slabs), kWarpsPerCta * 32, 0, st>>>(a);
 }
 
+// Narrow dense operand (N <= 64 floats, 16-byte aligned rows): a full warp per row would leave most
+// lanes idle, so a warp is cut into 32/LANES groups of LANES lanes and every group owns a row.  Lane t
+// of a group holds columns 4t..4t+3; the group's (column, value) pairs are fetched LANES at a time
+// (one per lane) and handed round with width-LANES shuffles; every B row segment is one 16-byte load
+// per lane, LANES*16 contiguous bytes per group.  Each output element still accumulates in CSR order.
+template <int LANES, bool STRICT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_subwarp_kernel(const SpmmArgs a)
+{
+    constexpr int kRowsPerWarp = 32 / LANES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane / LANES, t = lane % LANES;
+    const int slot = (blockIdx.x * kWarpsPerCta + warp) * kRowsPerWarp + g;
+    const bool has_row = slot < a.M;
+    const int row = has_row ? (a.row_order ? a.row_order[slot] : slot) : 0;
+    int start = 0, len = 0;
+    if (has_row) {
+        start = __ldg(a.row_offsets + row);
+        len = __ldg(a.row_offsets + row + 1) - start;
+    }
+    const bool active = has_row && t * 4 < a.N;
+    const int longest = __reduce_max_sync(0xffffffffu, len);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float *bcol = a.B + t * 4;
+    for (int base = 0; base < longest; base += LANES) {
+        int c = 0;
+        float v = 0.f;
+        if (base + t < len) {
+            c = __ldg(a.cols + start + base + t);
+            v = __ldg(a.values + start + base + t);
+        }
+#pragma unroll
+        for (int j = 0; j < LANES; j++) {
+            const int cj = __shfl_sync(0xffffffffu, c, j, LANES);
+            const float vj = __shfl_sync(0xffffffffu, v, j, LANES);
+            if (active && base + j < len) {
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(bcol + (size_t)cj * (size_t)a.N));
+                acc[0] = mad<STRICT>(vj, b.x, acc[0]);
+                acc[1] = mad<STRICT>(vj, b.y, acc[1]);
+                acc[2] = mad<STRICT>(vj, b.z, acc[2]);
+                acc[3] = mad<STRICT>(vj, b.w, acc[3]);
+            }
+        }
+    }
+    if (active)
+        *reinterpret_cast<float4 *>(a.C + (size_t)row * (size_t)a.N + t * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+template <int LANES>
+void launch_subwarp(const SpmmArgs &a, bool strict, cudaStream_t st)
+{
+    const int rows_per_block = kWarpsPerCta * (32 / LANES);
+    const unsigned blocks = (unsigned)dlspm_ceil_div(a.M, rows_per_block);
+    if (strict) spmm_subwarp_kernel<LANES, true><<<blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    else spmm_subwarp_kernel<LANES, false><<<blocks, kWarpsPerCta * 32, 0, st>>>(a);
+}
+
 template <int VEC, int U>
 void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
 {
@@ -189,7 +245,16 @@ int spmm_launch(dlspm_ctx *ctx, int M, int N, int nnz, const float *values, cons
     const int vec = dlspm_vec_width(N, B, C);
     const bool strict = ctx->strict_fp32 != 0;
     const int split = spmm_row_split(ctx, M, N, nnz, vec, strict);
-    if (vec == 4) launch_rows_vec<4>(a, split, strict, st);
+    // narrow N: several rows per warp, but never so many that the matrix yields too few warps
+    int lanes = 32;
+    if (vec == 4 && N <= 64 && split == 1) {
+        lanes = N <= 16 ? 4 : N <= 32 ? 8 : 16;
+        while (lanes < 32 && (long long)M * lanes / 32 < (long long)ctx->sm_count * 16) lanes *= 2;
+    }
+    if (lanes == 4) launch_subwarp<4>(a, strict, st);
+    else if (lanes == 8) launch_subwarp<8>(a, strict, st);
+    else if (lanes == 16) launch_subwarp<16>(a, strict, st);
+    else if (vec == 4) launch_rows_vec<4>(a, split, strict, st);
     else if (vec == 2) launch_rows_vec<2>(a, split, strict, st);
     else launch_rows_vec<1>(a, split, strict, st);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
