@@ -27,6 +27,8 @@ struct dlspm_ctx {
     cudaStream_t h2d_stream, d2h_stream;
     cudaEvent_t ev_h2d[2], ev_kernel[2], ev_d2h[2];
     int pipeline_ready;
+    void *pinned;  // pinned host memory for the launch tables of the pipelined batch
+    size_t pinned_bytes;
 };
 
 struct dlspm_plan {
@@ -61,7 +63,10 @@ int dlspm_stage_reserve(dlspm_ctx *ctx, size_t bytes);
 
 // One-shot grouped launch with caller-provided table memory (spmm.cu).
 size_t dlspm_batched_table_bytes(int count);
-int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st);
+// `pinned` (optional, host memory of the same size): the tables are built there and copied
+// asynchronously; the caller must not reuse it before the launch has finished.
+int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st,
+                          void *pinned = nullptr);
 
 static inline int dlspm_ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long dlspm_ceil_div64(long long a, long long b) { return (a + b - 1) / b; }

@@ -76,6 +76,7 @@ extern "C" int dlspm_destroy(dlspm_ctx *ctx)
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->pinned) cudaFreeHost(ctx->pinned);
     if (ctx->pipeline_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);

@@ -188,6 +188,19 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
     const size_t slot = padded(max_piece) + padded(max_tables);
     rc = dlspm_stage_reserve(ctx, 2 * slot + 256);
     if (rc) return rc;
+    // the launch tables travel from pinned memory: a copy from pageable memory would synchronise
+    // the compute stream with the host and serialise the pipeline
+    if (ctx->pinned_bytes < 2 * padded(max_tables)) {
+        if (ctx->pinned) cudaFreeHost(ctx->pinned);
+        ctx->pinned = nullptr;
+        ctx->pinned_bytes = 0;
+        cudaError_t perr = cudaMallocHost(&ctx->pinned, 2 * padded(max_tables));
+        if (perr != cudaSuccess) {
+            dlspm_cuda_fail(ctx, perr, "cudaMallocHost(tables)");
+            return DLSPM_ERR_NOMEM;
+        }
+        ctx->pinned_bytes = 2 * padded(max_tables);
+    }
     cudaStream_t h2d = ctx->h2d_stream, run = ctx->stream, d2h = ctx->d2h_stream;
     std::vector<dlspm_problem> dev[2];
     int first = 0;
@@ -195,8 +208,12 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
         const int last = piece_end[pi];
         const int b = (int)(pi & 1);
         char *base = (char *)ctx->stage + (size_t)b * slot;
-        // the slot is free once the results of the piece that used it two rounds ago have left
-        if (pi >= 2) DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(h2d, ctx->ev_d2h[b], 0));
+        // the slot is free once the results of the piece that used it two rounds ago have left;
+        // its pinned table may be rewritten once that piece's launch has finished
+        if (pi >= 2) {
+            DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(h2d, ctx->ev_d2h[b], 0));
+            DLSPM_CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev_kernel[b]));
+        }
         Carver cv(base + padded(max_tables));
         dev[b].clear();
         for (int i = first; i < last; i++) {
@@ -222,7 +239,8 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
         }
         DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_h2d[b], h2d));
         DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(run, ctx->ev_h2d[b], 0));
-        rc = dlspm_spmm_batched_at(ctx, (int)dev[b].size(), dev[b].data(), base, run);
+        rc = dlspm_spmm_batched_at(ctx, (int)dev[b].size(), dev[b].data(), base, run,
+                                   (char *)ctx->pinned + (size_t)b * padded(max_tables));
         if (rc) return rc;
         DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_kernel[b], run));
         DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(d2h, ctx->ev_kernel[b], 0));

@@ -959,7 +959,8 @@ size_t dlspm_batched_table_bytes(int count)
 
 // One-shot grouped launch with its tables placed at `tables` (device memory of at least
 // dlspm_batched_table_bytes(count) bytes, owned by the caller until the launch has finished).
-int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st)
+int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st,
+                          void *pinned)
 {
     std::vector<BatchProblem> tab;
     std::vector<long long> starts;
@@ -971,8 +972,15 @@ int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *proble
     const size_t st_bytes = sizeof(long long) * starts.size();
     const size_t cnt_off = st_off + ((sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255);
     char *base = (char *)tables;
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, tab.data(), tab_bytes, cudaMemcpyHostToDevice, st));
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, starts.data(), st_bytes, cudaMemcpyHostToDevice, st));
+    const void *src_tab = tab.data(), *src_starts = starts.data();
+    if (pinned) {
+        memcpy(pinned, tab.data(), tab_bytes);
+        memcpy((char *)pinned + st_off, starts.data(), st_bytes);
+        src_tab = pinned;
+        src_starts = (char *)pinned + st_off;
+    }
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, src_tab, tab_bytes, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, src_starts, st_bytes, cudaMemcpyHostToDevice, st));
     return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
                                (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
 }
