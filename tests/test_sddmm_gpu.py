@@ -49,6 +49,16 @@ def test_inner_dimensions(pkg, oracle, ctx, dev, N):
     check(oracle, ro, ci, lhs, rhs, M, N, run_sddmm(ctx, dev, M, K, N, ro, ci, lhs, rhs))
 
 
+@pytest.mark.parametrize("N", [1028, 2048, 2052, 3136, 4100])
+def test_long_inner_dimension_segments(pkg, oracle, ctx, dev, N):
+    """Inner dimensions above 1024 run in segments (512 or 1024 floats) with a ragged last segment."""
+    M, K = 70, 90
+    ro, ci = csr_bernoulli(pkg, M, K, 0.3, seed=700 + N)
+    lhs = dense(pkg, M, N, 700 + N, 11, kind=pkg.KIND_NORMAL)
+    rhs = dense(pkg, K, N, 700 + N, 12, kind=pkg.KIND_NORMAL)
+    check(oracle, ro, ci, lhs, rhs, M, N, run_sddmm(ctx, dev, M, K, N, ro, ci, lhs, rhs))
+
+
 def test_row_length_edges(pkg, oracle, ctx, dev):
     K, N = 150, 64
     lengths = [0, 1, 0, 7, 8, 9, 31, 32, 33, 64, 65, 150, 0, 2, 0]

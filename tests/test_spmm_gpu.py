@@ -62,6 +62,46 @@ def test_sweep_shapes(pkg, oracle, ctx, dev, shape, sparsity):
     check(oracle, ro, ci, vals, B, M, N, run_spmm(ctx, dev, M, K, N, ro, ci, vals, B))
 
 
+@pytest.mark.parametrize("N", [4, 8, 12, 16, 20, 32, 36, 48, 64])
+def test_narrow_dense_operand_many_rows(pkg, oracle, ctx, dev, N):
+    """Enough rows for the several-rows-per-warp kernel (N <= 64): 4, 8 and 16 lanes per row, widths
+    that do not fill the lane group, empty rows and rows longer than one fetch round."""
+    M, K = 40000, 96
+    seed = 600 + N
+    ro, ci = csr_rowlen_normal(pkg, M, K, 0.8, seed, cov=0.8)
+    assert (np.diff(ro) == 0).any() and np.diff(ro).max() > 32
+    vals = pkg.gen_dense_host(int(ci.size), seed, 2)
+    B = dense(pkg, K, N, seed, 10)
+    out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+    check(oracle, ro, ci, vals, B, M, N, out)
+    planned = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B, plan=True)
+    assert np.array_equal(out.view(np.uint32), planned.view(np.uint32))
+    if N in (16, 32, 64):
+        ctx.set_option(pkg.OPT_STRICT_FP32, 1)
+        try:
+            strict = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+        finally:
+            ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+        assert np.array_equal(strict.view(np.uint32), oracle.spmm(vals, ro, ci, B, M, N).view(np.uint32))
+
+
+def test_few_long_rows_shared_between_warps(pkg, oracle, ctx, dev):
+    """Few rows with many nonzeros: 2, 4 or 8 warps share a row; strict mode keeps one warp per row."""
+    for (M, K, N) in [(64, 4096, 256), (300, 2048, 132), (1024, 4096, 260), (9, 3000, 1024)]:
+        seed = M + N
+        ro, ci = csr_rowlen_normal(pkg, M, K, 0.7, seed)
+        vals = pkg.gen_dense_host(int(ci.size), seed, 2)
+        B = dense(pkg, K, N, seed, 10)
+        out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+        check(oracle, ro, ci, vals, B, M, N, out)
+        ctx.set_option(pkg.OPT_STRICT_FP32, 1)
+        try:
+            strict = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+        finally:
+            ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+        assert np.array_equal(strict.view(np.uint32), oracle.spmm(vals, ro, ci, B, M, N).view(np.uint32))
+
+
 def test_row_length_edges(pkg, oracle, ctx, dev):
     # empty rows first/last/in between, lengths around the 32-wide staging chunk, one full row
     K, N = 200, 132
