@@ -456,6 +456,38 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
         "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / ms,
         "binds": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (fp32_tflops * 1e12) else "fp32"}
     batch.close()
+
+    # shapes whose algorithmic intensity is below the fp32 ridge (HBM-bound on paper), many copies
+    # of one shape in a grouped launch, about 1.5 GB resident each
+    small = {}
+    for (M, K, N, sp) in ((64, 64, 1024, 0.9), (64, 64, 1024, 0.98), (64, 64, 3136, 0.98), (256, 256, 3136, 0.98)):
+        copies = int(min(3000, 1.5e9 / spmm_bytes(M, K, N, int(M * K * (1 - sp)))))
+        arr = pkg.ProblemArray(copies)
+        flops = nbytes = 0.0
+        for c in range(copies):
+            seed = 1000 * M + N + 7919 * c
+            ro = pkg.gen_rowlen_normal_host(M, K, sp, COV, seed)
+            nnz = int(ro[-1])
+            d_ro = up(ro)
+            d_ci = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)[:nnz]
+            ctx.gen_sample_columns(M, K, d_ro, seed, d_ci)
+            v = torch.empty(max(nnz, 1), device=dev)[:nnz]
+            ctx.gen_dense(v, seed, 2)
+            Bm = torch.empty(K * N, device=dev)
+            ctx.gen_dense(Bm, seed, 10)
+            arr.set(c, M, K, N, nnz, v, d_ro, d_ci, Bm, torch.empty(M * N, device=dev))
+            flops += 2.0 * nnz * N
+            nbytes += spmm_bytes(M, K, N, nnz)
+        batch = ctx.batch_create(arr)
+        batch.launch()
+        torch.cuda.synchronize()
+        ms = st.median(time_kernel(batch.launch, 5))
+        batch.close()
+        small[f"{M}x{K}_n{N}_s{sp}"] = {"copies": copies, "us_per_problem": ms * 1e3 / copies,
+                                        "gflops": flops / ms * 1e-6, "hbm_gbs": nbytes / ms * 1e-6,
+                                        "hbm_frac": nbytes / ms * 1e-6 / hbm_gbs}
+        del arr
+    out["spmm_hbm_bound_shapes_batched"] = small
     del flush
     return out
 
