@@ -648,6 +648,20 @@ def main():
     weights = np.array([float(d[5][-1]) * d[2] for d in descs])
     sharding = __import__("importlib").import_module(entry.PKG_NAME + ".sharding")
     mine = sharding.my_problems(pkg, weights, rank, world)
+    # the batch must fit the memory that is free on this GPU (113 GiB for all 8192 problems on one
+    # GPU); if it does not, every rank drops the same tail of the batch and the line says so
+    need = sum(4.0 * (descs[i][0] + 1 + 2 * float(descs[i][5][-1]) + descs[i][1] * descs[i][2] + descs[i][0] * descs[i][2])
+               for i in mine)
+    free_bytes, _total = torch.cuda.mem_get_info(dev)
+    fit = torch.tensor([min(1.0, 0.85 * free_bytes / max(need, 1.0))], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(fit, op=dist.ReduceOp.MIN)
+    if float(fit[0]) < 1.0:
+        args.problems = max(world, int(args.problems * float(fit[0])))
+        log(f"[rank {rank}] batch cut to {args.problems} problems to fit device memory")
+        descs = descs[:args.problems]
+        weights = weights[:args.problems]
+        mine = sharding.my_problems(pkg, weights, rank, world)
     batch = DeviceBatch(pkg, ctx, dev, descs, mine)
     n_gather, n_tiled, _ = batch.batch.info()
     part_stats = list(batch.batch.stats)
