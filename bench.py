@@ -613,7 +613,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--tile-density", type=int, default=None, help="DLSPM_OPT_TILE_MIN_DENSITY in thousandths")
-    ap.add_argument("--spmm-kernel", type=int, default=0, help="0 auto, 1 row-gather only, 2 tiled where possible")
+    ap.add_argument("--spmm-kernel", type=int, default=0, help="0 auto, 1 row-gather only, 2 tiled where possible, 3 tiled with zeros")
     ap.add_argument("--e2e-bytes", type=float, default=2e9, help="host bytes of the e2e sample per rank")
     args = ap.parse_args()
 

@@ -109,7 +109,7 @@ extern "C" int dlspm_set_option(dlspm_ctx *ctx, int option, int value)
     switch (option) {
     case DLSPM_OPT_STRICT_FP32: ctx->strict_fp32 = value ? 1 : 0; return DLSPM_OK;
     case DLSPM_OPT_SPMM_KERNEL:
-        if (value < 0 || value > 2) return DLSPM_ERR_INVALID_ARGUMENT;
+        if (value < 0 || value > 3) return DLSPM_ERR_INVALID_ARGUMENT;
         ctx->spmm_kernel = value;
         return DLSPM_OK;
     case DLSPM_OPT_TILE_MIN_DENSITY:

@@ -761,15 +761,24 @@ int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long
     static bool attr_set[64];
     const size_t smem = sizeof(TileSmem);
     if (ctx->device < 64 && !attr_set[ctx->device]) {
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[ctx->device] = true;
     }
     DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
     const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 2);
     dim3 grid((unsigned)want), block(kTileThreads);
-    if (ctx->strict_fp32) spmm_tile_kernel<true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
-    else spmm_tile_kernel<false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    // kernel choice 3: absent entries are multiplied as zeros (no mask tests in the inner loop)
+    const bool dense = ctx->spmm_kernel == 3;
+    if (dense) {
+        if (ctx->strict_fp32) spmm_tile_kernel<true, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+        else spmm_tile_kernel<false, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    } else {
+        if (ctx->strict_fp32) spmm_tile_kernel<true, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+        else spmm_tile_kernel<false, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    }
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
@@ -780,8 +789,10 @@ int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long
 bool prefer_tiled(const dlspm_ctx *ctx, const dlspm_problem &q, int vec, bool sorted)
 {
     if (ctx->spmm_kernel == 1 || vec != 4 || !sorted || q.nnz == 0) return false;
-    if (ctx->spmm_kernel == 2) return true;
     const double density = (double)q.nnz / ((double)q.M * (double)q.K);
+    // choices 2 and 3 take every eligible problem unless a density threshold was set as well
+    if (ctx->spmm_kernel >= 2)
+        return ctx->tile_min_density_permille > 1000 || density * 1000.0 >= (double)ctx->tile_min_density_permille;
     return density * 1000.0 >= (double)ctx->tile_min_density_permille && q.M >= 16 && q.N >= 64;
 }
 

@@ -124,6 +124,8 @@ __device__ __forceinline__ void tile_fetch_candidates(TileSmem &sm, const TilePr
 }
 
 // Scatters the fetched entries that fall into columns [k0, k0+32) into As[s] and writes the masks.
+// DENSE: absent entries are written as zeros, so that the inner loop can run without mask tests.
+template <bool DENSE>
 __device__ __forceinline__ void tile_expand_a(TileSmem &sm, int s, int k0, int warp, int lane)
 {
     cp_async_wait_all();
@@ -139,6 +141,10 @@ __device__ __forceinline__ void tile_expand_a(TileSmem &sm, int s, int k0, int w
             v = sm.cand_val[r][lane];
         }
         const bool take = (unsigned)c < (unsigned)kTileK;  // columns ascend: the taken ones are a prefix
+        if constexpr (DENSE) {
+            sm.As[s][r][lane] = 0.f;
+            __syncwarp();
+        }
         if (take) sm.As[s][r][c] = v;
         const unsigned mask = __reduce_or_sync(0xffffffffu, take ? (1u << c) : 0u);
         if (lane == 0) {
@@ -171,7 +177,7 @@ __device__ __forceinline__ void row_update(float (&acc)[8], float av, const floa
 
 // Persistent thread blocks pull tile numbers from `counter`; tile_start[i] is the first tile of
 // problem i.  On an mbarrier timeout error[0] is set to 1 and the block returns.
-template <bool STRICT>
+template <bool STRICT, bool DENSE>
 __global__ void __launch_bounds__(kTileThreads, 2)
 spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__restrict__ tile_start, int count,
                  unsigned long long *counter, int *error)
@@ -230,7 +236,7 @@ spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__re
         const int nchunks = (p.K + kTileK - 1) / kTileK;
         if (warp == 0) tile_load_b(sm, p, 0, 0, n0, lane);
         tile_fetch_candidates(sm, p, warp, lane);
-        tile_expand_a(sm, 0, 0, warp, lane);
+        tile_expand_a<DENSE>(sm, 0, 0, warp, lane);
 
         bool aborted = false;
         for (int c = 0; c < nchunks; c++) {
@@ -247,6 +253,25 @@ spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__re
             if (s) phase1 ^= 1u;
             else phase0 ^= 1u;
 
+            if constexpr (DENSE) {
+                // every entry of the 8 x 32 block is multiplied; absent ones are zeros
+#pragma unroll 2
+                for (int k4 = 0; k4 < kTileK; k4 += 4) {
+                    float4 a[kTileRowsPerWarp];
+#pragma unroll
+                    for (int i = 0; i < kTileRowsPerWarp; i++) a[i] = *reinterpret_cast<const float4 *>(&sm.As[s][wr + i][k4]);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        const float4 b0 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][lane * 4]);
+                        const float4 b1 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][128 + lane * 4]);
+#pragma unroll
+                        for (int i = 0; i < kTileRowsPerWarp; i++) {
+                            const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
+                            row_update<STRICT>(acc[i], av, b0, b1);
+                        }
+                    }
+                }
+            } else {
             unsigned m[kTileRowsPerWarp];
             unsigned any = 0;
 #pragma unroll
@@ -278,7 +303,8 @@ spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__re
                     }
                 }
             }
-            if (more) tile_expand_a(sm, s ^ 1, (c + 1) * kTileK, warp, lane);
+            }
+            if (more) tile_expand_a<DENSE>(sm, s ^ 1, (c + 1) * kTileK, warp, lane);
             __syncthreads();  // every warp is done with Bs[s]: it may be refilled in the next round
             if (*(volatile int *)&sm.abort) {
                 aborted = true;

@@ -277,6 +277,11 @@ def test_tiled_kernel_matches_gather_and_oracle(pkg, oracle, ctx, dev):
     # absent entries add fma(0, b, acc) = acc: the tiled kernel has the bits of the row-gather kernel
     for a, b in zip(tiled, gather):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # the variant that multiplies absent entries as zeros: same bits on finite data
+    dense, info_d = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_TILED_DENSE)
+    assert info_d[1] == len(probs) and info_d[2] == 0
+    for a, b in zip(dense, gather):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
 def test_tiled_kernel_strict_mode_is_bit_exact(pkg, oracle, ctx, dev):
