@@ -80,3 +80,14 @@ static inline int dlspm_vec_width(int N, const void *p0, const void *p1, const v
     if ((N % 2 == 0) && (bits % 8 == 0)) return 2;
     return 1;
 }
+
+// Argument check shared by the SpMM entry points.
+static inline int check_spmm_args(int M, int K, int N, int nnz, const float *values, const int *row_offsets,
+                    const int *cols, const float *B, float *C)
+{
+    if (M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0 && (!values || !cols || !B)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (M > 0 && N > 0 && !C) return DLSPM_ERR_INVALID_ARGUMENT;
+    return DLSPM_OK;
+}

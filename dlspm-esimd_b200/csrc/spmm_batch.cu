@@ -1,0 +1,596 @@
+// Grouped launch over many independent SpMMs for sm_100a: the persistent row-gather kernel that pulls
+// tiles from a device counter, the analysis of a batch (row order by length, sortedness), prepared
+// batches with the optional tiled kernel, the one-shot launch and the variant that allocates nothing.
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "spmm_device.cuh"
+#include "spmm_tile.cuh"
+
+using namespace dlspm;
+
+// ---- grouped launch ---------------------------------------------------------------------------
+namespace {
+
+struct BatchProblem {
+    const float *values;
+    const int *row_offsets;
+    const int *cols;
+    const float *B;
+    float *C;
+    int M, N;
+    int row_groups;
+    int vec;     // 1, 2 or 4
+    int chunks;  // column chunks per slab: 1, 2 or 4
+    int K;
+    const int *row_order;  // rows from the longest to the shortest (nullptr: natural order)
+    int nnz;
+    int pad;
+};
+
+template <int VEC, bool STRICT>
+__device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, int row, int start,
+                                             int end, int lane, int2 *stage)
+{
+    float *Crow = p.C + (size_t)row * (size_t)p.N;
+    const int n0 = slab * 32 * VEC * p.chunks;
+    if (p.chunks == 4)
+        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+    else if (p.chunks == 2)
+        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+    else
+        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+}
+
+// Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
+// tile of problem i (problems are stored from the most to the least work), tile_start[count] the
+// total.
+template <bool STRICT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *__restrict__ tile_start,
+                    int count, unsigned long long *counter)
+{
+    __shared__ int2 stage[kWarpsPerCta][32];
+    __shared__ unsigned long long s_tile;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long total = tile_start[count];
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(counter, 1ull);
+        __syncthreads();
+        const long long tile = (long long)s_tile;
+        __syncthreads();
+        if (tile >= total) break;
+        int lo = 0, hi = count - 1;  // last problem whose first tile is <= tile
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(tile_start + mid) <= tile) lo = mid;
+            else hi = mid - 1;
+        }
+        const BatchProblem p = problems[lo];
+        const long long t = tile - __ldg(tile_start + lo);
+        const int slab = (int)(t / p.row_groups);
+        const int slot = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
+        if (slot < p.M) {
+            const int row = p.row_order ? __ldg(p.row_order + slot) : slot;
+            const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+            if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+            else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+            else batched_tile<1, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+        }
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// Builds the host-side tables for a batch: problems ordered by decreasing nnz*N.
+int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProblem> &tab,
+                 std::vector<long long> &starts)
+{
+    std::vector<int> order;
+    order.reserve(count);
+    for (int i = 0; i < count; i++) {
+        const dlspm_problem &q = problems[i];
+        int rc = check_spmm_args(q.M, q.K, q.N, q.nnz, q.values, q.row_offsets, q.column_indices,
+                                 q.B, q.C);
+        if (rc) return rc;
+        if (q.M > 0 && q.N > 0) order.push_back(i);
+    }
+    std::stable_sort(order.begin(), order.end(), [&](int x, int y) {
+        return (double)problems[x].nnz * problems[x].N > (double)problems[y].nnz * problems[y].N;
+    });
+    tab.clear();
+    starts.clear();
+    long long run = 0;
+    for (int i : order) {
+        const dlspm_problem &q = problems[i];
+        BatchProblem b;
+        b.values = q.values;
+        b.row_offsets = q.row_offsets;
+        b.cols = q.column_indices;
+        b.B = q.B;
+        b.C = q.C;
+        b.M = q.M;
+        b.N = q.N;
+        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+        b.vec = dlspm_vec_width(q.N, q.B, q.C);
+        b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.K = q.K;
+        b.row_order = nullptr;
+        b.nnz = q.nnz;
+        b.pad = 0;
+        starts.push_back(run);
+        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
+        tab.push_back(b);
+    }
+    starts.push_back(run);
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+// ---- analysis of a batch: row order by length and sortedness, one thread block per problem -------
+namespace {
+
+constexpr int kLenBins = 4096;  // counting sort on min(row length, 4095)
+
+// flags[i] bit 0: every row of problem i has strictly ascending columns.
+__global__ void __launch_bounds__(256) batch_analyze_kernel(const BatchProblem *__restrict__ problems, int count,
+                                                           int *__restrict__ flags)
+{
+    __shared__ int hist[kLenBins];
+    __shared__ int warp_tot[8];
+    __shared__ int s_sorted;
+    for (int pi = blockIdx.x; pi < count; pi += gridDim.x) {
+        const BatchProblem p = problems[pi];
+        for (int b = threadIdx.x; b < kLenBins; b += blockDim.x) hist[b] = 0;
+        if (threadIdx.x == 0) s_sorted = 1;
+        __syncthreads();
+        bool sorted = true;
+        for (int r = threadIdx.x; r < p.M; r += blockDim.x) {
+            const int s = p.row_offsets[r], e = p.row_offsets[r + 1];
+            atomicAdd(&hist[min(max(e - s, 0), kLenBins - 1)], 1);
+            for (int q = s + 1; q < e; q++) sorted &= p.cols[q - 1] < p.cols[q];
+        }
+        if (!sorted) s_sorted = 0;
+        __syncthreads();
+        // exclusive scan over the bins from the longest to the shortest: 16 bins per thread
+        const int per = kLenBins / 256;
+        int local[per];
+        int sum = 0;
+        for (int i = 0; i < per; i++) {
+            local[i] = hist[kLenBins - 1 - (threadIdx.x * per + i)];
+            sum += local[i];
+        }
+        int incl = sum;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((threadIdx.x & 31) >= d) incl += o;
+        }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        int before = incl - sum;
+        for (int w = 0; w < (int)(threadIdx.x >> 5); w++) before += warp_tot[w];
+        __syncthreads();
+        for (int i = 0; i < per; i++) {
+            hist[kLenBins - 1 - (threadIdx.x * per + i)] = before;  // first slot of the bin
+            before += local[i];
+        }
+        __syncthreads();
+        if (p.row_order) {
+            int *order = const_cast<int *>(p.row_order);
+            for (int r = threadIdx.x; r < p.M; r += blockDim.x) {
+                const int len = p.row_offsets[r + 1] - p.row_offsets[r];
+                order[atomicAdd(&hist[min(max(len, 0), kLenBins - 1)], 1)] = r;
+            }
+        }
+        if (threadIdx.x == 0) flags[pi] = s_sorted;
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+struct dlspm_batch {
+    dlspm_ctx *ctx;
+    // row-gather part
+    int count;
+    long long tiles;
+    BatchProblem *problems;       // device
+    long long *tile_start;        // device, count + 1
+    // tiled part (denser problems)
+    int tcount;
+    long long ttiles;
+    TileProblem *tproblems;       // device
+    long long *ttile_start;       // device, tcount + 1
+    unsigned long long *counters; // device: [0] row-gather, [1] tiled
+    int *row_order_pool;          // device: row orders of all row-gather problems
+    int *error;                   // device: set by a kernel whose bounded wait ran out
+    double stats[4];              // 2*nnz*N and algorithmic bytes: row-gather part, tiled part
+};
+
+namespace {
+
+int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long long *d_starts,
+                        unsigned long long *d_counter, int count, long long tiles, cudaStream_t st)
+{
+    if (count == 0 || tiles == 0) return DLSPM_OK;
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 8);
+    dim3 grid((unsigned)want), block(kWarpsPerCta * 32);
+    if (ctx->strict_fp32) spmm_batched_kernel<true><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
+    else spmm_batched_kernel<false><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long *d_starts,
+                       unsigned long long *d_counter, int *d_error, int count, long long tiles, cudaStream_t st)
+{
+    if (count == 0 || tiles == 0) return DLSPM_OK;
+    static bool attr_set[64];
+    const size_t smem = sizeof(TileSmem);
+    if (ctx->device < 64 && !attr_set[ctx->device]) {
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[ctx->device] = true;
+    }
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 2);
+    dim3 grid((unsigned)want), block(kTileThreads);
+    // kernel choice 3: absent entries are multiplied as zeros (no mask tests in the inner loop)
+    const bool dense = ctx->spmm_kernel == 3;
+    if (dense) {
+        if (ctx->strict_fp32) spmm_tile_kernel<true, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+        else spmm_tile_kernel<false, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    } else {
+        if (ctx->strict_fp32) spmm_tile_kernel<true, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+        else spmm_tile_kernel<false, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
+    }
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+// Kernel choice for one problem of a prepared batch.  The tiled kernel needs 16-byte aligned rows
+// of B and C (N % 4 == 0) and strictly ascending columns; it pays off once a B row loaded into shared
+// memory is used by more than one of a warp's 8 rows often enough, i.e. from a density threshold.
+bool prefer_tiled(const dlspm_ctx *ctx, const dlspm_problem &q, int vec, bool sorted)
+{
+    if (ctx->spmm_kernel == 1 || vec != 4 || !sorted || q.nnz == 0) return false;
+    const double density = (double)q.nnz / ((double)q.M * (double)q.K);
+    // choices 2 and 3 take every eligible problem unless a density threshold was set as well
+    if (ctx->spmm_kernel >= 2)
+        return ctx->tile_min_density_permille > 1000 || density * 1000.0 >= (double)ctx->tile_min_density_permille;
+    return density * 1000.0 >= (double)ctx->tile_min_density_permille && q.M >= 16 && q.N >= 64;
+}
+
+}  // namespace
+
+extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                  dlspm_batch **out)
+{
+    if (!ctx || !out || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    std::vector<BatchProblem> tab;
+    std::vector<long long> starts;
+    rc = build_tables(count, problems, tab, starts);  // validates; all problems, most work first
+    if (rc) return rc;
+    dlspm_batch *b = new (std::nothrow) dlspm_batch();
+    if (!b) return DLSPM_ERR_NOMEM;
+    memset(b, 0, sizeof(*b));
+    b->ctx = ctx;
+    const size_t n = tab.size();
+    // pass 1: analyse every problem on the device (row order by length, sortedness)
+    size_t rows_total = 0;
+    for (const BatchProblem &t : tab) rows_total += (size_t)t.M;
+    int *d_flags = nullptr;
+    BatchProblem *d_all = nullptr;
+    std::vector<int> flags(n, 0);
+    cudaError_t err = cudaMalloc(&b->row_order_pool, sizeof(int) * std::max<size_t>(rows_total, 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->counters, 2 * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMalloc(&b->error, sizeof(int));
+    if (err == cudaSuccess) err = cudaMemset(b->error, 0, sizeof(int));
+    if (err == cudaSuccess && n) {
+        size_t off = 0;
+        for (BatchProblem &t : tab) {
+            t.row_order = b->row_order_pool + off;
+            off += (size_t)t.M;
+        }
+        err = cudaMalloc(&d_all, sizeof(BatchProblem) * n);
+        if (err == cudaSuccess) err = cudaMalloc(&d_flags, sizeof(int) * n);
+        if (err == cudaSuccess) err = cudaMemcpy(d_all, tab.data(), sizeof(BatchProblem) * n, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) {
+            const int blocks = (int)std::min<size_t>(n, (size_t)ctx->sm_count * 8);
+            batch_analyze_kernel<<<blocks, 256>>>(d_all, (int)n, d_flags);
+            err = cudaMemcpy(flags.data(), d_flags, sizeof(int) * n, cudaMemcpyDeviceToHost);
+        }
+        if (d_flags) cudaFree(d_flags);
+        if (d_all) cudaFree(d_all);
+    }
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "batch analysis");
+        dlspm_batch_destroy(b);
+        return DLSPM_ERR_CUDA;
+    }
+    // pass 2: split into the tiled and the row-gather tables
+    std::vector<BatchProblem> gtab;
+    std::vector<long long> gstarts;
+    std::vector<TileProblem> ttab;
+    std::vector<long long> tstarts;
+    long long grun = 0, trun = 0;
+    for (size_t i = 0; i < n; i++) {
+        const BatchProblem &t = tab[i];
+        dlspm_problem q;
+        q.M = t.M; q.K = t.K; q.N = t.N;
+        q.nnz = t.nnz;
+        const double fl = 2.0 * (double)t.nnz * t.N;
+        const double by = 4.0 * (t.M + 1) + 8.0 * t.nnz + 4.0 * (double)t.K * t.N + 4.0 * (double)t.M * t.N;
+        const bool tiled = prefer_tiled(ctx, q, t.vec, flags[i] & 1);
+        b->stats[tiled ? 2 : 0] += fl;
+        b->stats[tiled ? 3 : 1] += by;
+        if (tiled) {
+            TileProblem tp;
+            tp.values = t.values; tp.row_offsets = t.row_offsets; tp.cols = t.cols; tp.B = t.B; tp.C = t.C;
+            tp.row_order = t.row_order;
+            tp.M = t.M; tp.K = t.K; tp.N = t.N;
+            tp.row_blocks = dlspm_ceil_div(t.M, kTileM);
+            tp.col_blocks = dlspm_ceil_div(t.N, kTileN);
+            tp.pad = 0;
+            tstarts.push_back(trun);
+            trun += (long long)tp.row_blocks * tp.col_blocks;
+            ttab.push_back(tp);
+        } else {
+            gstarts.push_back(grun);
+            grun += (long long)t.row_groups * dlspm_ceil_div(t.N, 32 * t.vec * t.chunks);
+            gtab.push_back(t);
+        }
+    }
+    gstarts.push_back(grun);
+    tstarts.push_back(trun);
+    b->count = (int)gtab.size();
+    b->tiles = grun;
+    b->tcount = (int)ttab.size();
+    b->ttiles = trun;
+    err = cudaMalloc(&b->problems, sizeof(BatchProblem) * std::max<size_t>(gtab.size(), 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->tile_start, sizeof(long long) * gstarts.size());
+    if (err == cudaSuccess) err = cudaMalloc(&b->tproblems, sizeof(TileProblem) * std::max<size_t>(ttab.size(), 1));
+    if (err == cudaSuccess) err = cudaMalloc(&b->ttile_start, sizeof(long long) * tstarts.size());
+    if (err == cudaSuccess && !gtab.empty())
+        err = cudaMemcpy(b->problems, gtab.data(), sizeof(BatchProblem) * gtab.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(b->tile_start, gstarts.data(), sizeof(long long) * gstarts.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess && !ttab.empty())
+        err = cudaMemcpy(b->tproblems, ttab.data(), sizeof(TileProblem) * ttab.size(), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(b->ttile_start, tstarts.data(), sizeof(long long) * tstarts.size(), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) {
+        dlspm_cuda_fail(ctx, err, "batch tables");
+        dlspm_batch_destroy(b);
+        return DLSPM_ERR_CUDA;
+    }
+    *out = b;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_batch_launch_part(dlspm_ctx *ctx, const dlspm_batch *batch, int part, void *stream)
+{
+    if (!ctx || !batch || batch->ctx != ctx || part < 0 || part > 2) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (part != 1) {
+        rc = tile_launch_tables(ctx, batch->tproblems, batch->ttile_start, batch->counters + 1, batch->error,
+                                batch->tcount, batch->ttiles, st);
+        if (rc) return rc;
+    }
+    if (part != 2) {
+        rc = batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counters, batch->count,
+                                 batch->tiles, st);
+    }
+    return rc;
+}
+
+extern "C" int dlspm_batch_launch(dlspm_ctx *ctx, const dlspm_batch *batch, void *stream)
+{
+    return dlspm_batch_launch_part(ctx, batch, 0, stream);
+}
+
+// Number of problems served by each kernel (for reports) and the device-side error word.
+extern "C" int dlspm_batch_info(dlspm_ctx *ctx, const dlspm_batch *batch, int *gather_problems,
+                                int *tiled_problems, int *device_error, double *stats4)
+{
+    if (!ctx || !batch || batch->ctx != ctx) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (gather_problems) *gather_problems = batch->count;
+    if (tiled_problems) *tiled_problems = batch->tcount;
+    if (stats4) memcpy(stats4, batch->stats, sizeof(batch->stats));
+    if (device_error) {
+        DLSPM_CUDA_TRY(ctx, cudaDeviceSynchronize());
+        DLSPM_CUDA_TRY(ctx, cudaMemcpy(device_error, batch->error, sizeof(int), cudaMemcpyDeviceToHost));
+    }
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_batch_destroy(dlspm_batch *b)
+{
+    if (!b) return DLSPM_OK;
+    cudaSetDevice(b->ctx->device);
+    if (b->problems) cudaFree(b->problems);
+    if (b->tile_start) cudaFree(b->tile_start);
+    if (b->tproblems) cudaFree(b->tproblems);
+    if (b->ttile_start) cudaFree(b->ttile_start);
+    if (b->counters) cudaFree(b->counters);
+    if (b->row_order_pool) cudaFree(b->row_order_pool);
+    if (b->error) cudaFree(b->error);
+    (void)cudaGetLastError();
+    delete b;
+    return DLSPM_OK;
+}
+
+// Bytes of device memory the tables of a one-shot grouped launch of `count` problems need.
+size_t dlspm_batched_table_bytes(int count)
+{
+    const size_t tab = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
+    const size_t st = (sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255;
+    return tab + st + 256;
+}
+
+// One-shot grouped launch with its tables placed at `tables` (device memory of at least
+// dlspm_batched_table_bytes(count) bytes, owned by the caller until the launch has finished).
+int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st,
+                          void *pinned)
+{
+    std::vector<BatchProblem> tab;
+    std::vector<long long> starts;
+    int rc = build_tables(count, problems, tab, starts);
+    if (rc) return rc;
+    if (tab.empty()) return DLSPM_OK;
+    const size_t tab_bytes = sizeof(BatchProblem) * tab.size();
+    const size_t st_off = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
+    const size_t st_bytes = sizeof(long long) * starts.size();
+    const size_t cnt_off = st_off + ((sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255);
+    char *base = (char *)tables;
+    const void *src_tab = tab.data(), *src_starts = starts.data();
+    if (pinned) {
+        memcpy(pinned, tab.data(), tab_bytes);
+        memcpy((char *)pinned + st_off, starts.data(), st_bytes);
+        src_tab = pinned;
+        src_starts = (char *)pinned + st_off;
+    }
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, src_tab, tab_bytes, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, src_starts, st_bytes, cudaMemcpyHostToDevice, st));
+    return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
+                               (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
+}
+
+// One-shot grouped launch: tables go to the context's scratch (no allocation once it is large
+// enough).  The table copies are stream-ordered cudaMemcpyAsync calls from pageable memory, which
+// return once the source has been read, so the host vectors may go out of scope.
+extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                      void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (count == 0) return DLSPM_OK;
+    rc = dlspm_scratch_reserve(ctx, dlspm_batched_table_bytes(count));
+    if (rc) return rc;
+    return dlspm_spmm_batched_at(ctx, count, problems, ctx->scratch, (cudaStream_t)stream);
+}
+
+// ---- grouped launch without any allocation ------------------------------------------------------
+// Some callers may not allocate device memory at the point where they need a grouped SpMM: a
+// plug-in running under a host framework that owns the device heap and hands out fixed buffers, a
+// real-time loop that must not take the allocator's lock, or code that runs after the heap has been
+// sized to the last byte.  dlspm_spmm_batched_f32 keeps its problem table, tile index and work
+// counter in context scratch that grows with cudaMalloc on demand; the variant below keeps them in
+// a fixed array that is part of the library image instead, so the call never allocates.  The price
+// is a hard limit on the batch size, and that every GPU which loads the library carries the array
+// (about 73 KiB) until the process exits.
+namespace {
+
+constexpr int kStaticMaxProblems = 1024;
+constexpr size_t kStaticTableBytes = sizeof(BatchProblem) * kStaticMaxProblems;
+constexpr size_t kStaticStartsOff = (kStaticTableBytes + 255) & ~(size_t)255;
+constexpr size_t kStaticStartsBytes = sizeof(long long) * (kStaticMaxProblems + 1);
+constexpr size_t kStaticCounterOff = (kStaticStartsOff + kStaticStartsBytes + 255) & ~(size_t)255;
+constexpr size_t kStaticScratchBytes = kStaticCounterOff + 256;
+
+// Problem table, tile index and work counter of dlspm_spmm_batched_f32_static.  In host code this
+// name is only a handle for cudaGetSymbolAddress, never an address a kernel can use.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices];  // device address of g_static_scratch, per device
+bool g_static_scratch_ready[kMaxDevices];
+
+// Looks up the device address of the static scratch on the context's device (which is current),
+// once per device.
+int static_scratch_address(dlspm_ctx *ctx, unsigned char **out)
+{
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return DLSPM_ERR_UNSUPPORTED;
+    if (!g_static_scratch_ready[ctx->device]) {
+        void *p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaGetSymbolAddress(g_static_scratch)");
+        g_static_scratch_addr[ctx->device] = p;
+        g_static_scratch_ready[ctx->device] = true;
+    }
+    *out = (unsigned char *)g_static_scratch_addr[ctx->device];
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
+                                             void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (count > kStaticMaxProblems) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "dlspm_spmm_batched_f32_static: %d problems exceed the fixed limit of %d", count,
+                 kStaticMaxProblems);
+        return DLSPM_ERR_UNSUPPORTED;
+    }
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    unsigned char *base = nullptr;
+    rc = static_scratch_address(ctx, &base);
+    if (rc) return rc;
+
+    // Host tables on the stack (no heap either): same order as the allocating entry point,
+    // decreasing nnz*N with the lower index first on ties.
+    BatchProblem tab[kStaticMaxProblems];
+    long long starts[kStaticMaxProblems + 1];
+    int order[kStaticMaxProblems];
+    int used = 0;
+    for (int i = 0; i < count; i++) {
+        const dlspm_problem &q = problems[i];
+        rc = check_spmm_args(q.M, q.K, q.N, q.nnz, q.values, q.row_offsets, q.column_indices, q.B, q.C);
+        if (rc) return rc;
+        if (q.M > 0 && q.N > 0) order[used++] = i;
+    }
+    if (used == 0) return DLSPM_OK;
+    std::sort(order, order + used, [&](int x, int y) {
+        const double wx = (double)problems[x].nnz * problems[x].N, wy = (double)problems[y].nnz * problems[y].N;
+        return wx != wy ? wx > wy : x < y;
+    });
+    long long run = 0;
+    for (int s = 0; s < used; s++) {
+        const dlspm_problem &q = problems[order[s]];
+        BatchProblem &b = tab[s];
+        b.values = q.values;
+        b.row_offsets = q.row_offsets;
+        b.cols = q.column_indices;
+        b.B = q.B;
+        b.C = q.C;
+        b.M = q.M;
+        b.N = q.N;
+        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+        b.vec = dlspm_vec_width(q.N, q.B, q.C);
+        b.chunks = spmm_slab_chunks(q.N, b.vec);
+        b.K = q.K;
+        b.row_order = nullptr;
+        b.nnz = q.nnz;
+        b.pad = 0;
+        starts[s] = run;
+        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
+    }
+    starts[used] = run;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    BatchProblem *d_tab = (BatchProblem *)base;
+    long long *d_starts = (long long *)(base + kStaticStartsOff);
+    unsigned long long *d_counter = (unsigned long long *)(base + kStaticCounterOff);
+    // The array keeps what the previous call left in it: the tables are overwritten here and the
+    // work counter is cleared by batch_launch_tables before the kernel starts.
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_tab, tab, sizeof(BatchProblem) * (size_t)used, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_starts, starts, sizeof(long long) * ((size_t)used + 1), cudaMemcpyHostToDevice, st));
+    return batch_launch_tables(ctx, d_tab, d_starts, d_counter, used, run, st);
+}
