@@ -401,6 +401,13 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
     out["fused_band4096_d64"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 4.0 * nnz * N,
                                           4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N, hbm_gbs, fp32_tflops)
 
+    # the same chain as sparse attention: scale 1/sqrt(d) and a row softmax between the two products
+    fn = lambda: ctx.attention(M, K, N, nnz, *f, scale=N ** -0.5, flags=pkg.ATTN_SOFTMAX)
+    fn(); fn()
+    out["attention_softmax_band4096_d64"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 4.0 * nnz * N,
+                                                      4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N,
+                                                      hbm_gbs, fp32_tflops)
+
     # the 90 % sparsity column of the sweep: 5 shapes x 3 widths
     sweep = {}
     for (M, K) in SHAPES:

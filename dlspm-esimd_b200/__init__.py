@@ -26,6 +26,7 @@ OK = 0
  ERR_TIMEOUT) = range(1, 10)
 OPT_STRICT_FP32, OPT_SPMM_KERNEL, OPT_TILE_MIN_DENSITY = 0, 1, 2
 SPMM_KERNEL_AUTO, SPMM_KERNEL_GATHER, SPMM_KERNEL_TILED, SPMM_KERNEL_TILED_DENSE = 0, 1, 2, 3
+ATTN_SOFTMAX = 1
 KIND_UNIFORM_PM1, KIND_UNIFORM_01, KIND_NORMAL = 0, 1, 2
 
 
@@ -61,6 +62,7 @@ _SIGNATURES = {
     "dlspm_spmm_csr_f32_planned": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P]),
     "dlspm_sddmm_csr_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "dlspm_fused_sddmm_spmm_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "dlspm_fused_attention_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, C.c_float, C.c_uint, _P]),
     "dlspm_plan_create": (_I, [_P, _I, _I, _I, _P, _P, _P, C.POINTER(_P)]),
     "dlspm_plan_destroy": (_I, [_P]),
     "dlspm_spmm_batched_f32": (_I, [_P, _I, C.POINTER(Problem), _P]),
@@ -77,6 +79,14 @@ _SIGNATURES = {
     "dlspm_read_smtx_host": (_I, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I),
                                   C.POINTER(C.POINTER(_I)), C.POINTER(C.POINTER(_I))]),
     "dlspm_write_smtx_host": (_I, [C.c_char_p, _I, _I, _I, _P, _P]),
+    "dlspm_read_smtx_values_host": (_I, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I),
+                                         C.POINTER(C.POINTER(_I)), C.POINTER(C.POINTER(_I)),
+                                         C.POINTER(C.POINTER(C.c_float))]),
+    "dlspm_write_smtx_values_host": (_I, [C.c_char_p, _I, _I, _I, _P, _P, _P]),
+    "dlspm_read_csr_cache_host": (_I, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I),
+                                       C.POINTER(C.POINTER(_I)), C.POINTER(C.POINTER(_I)),
+                                       C.POINTER(C.POINTER(C.c_float))]),
+    "dlspm_write_csr_cache_host": (_I, [C.c_char_p, _I, _I, _I, _P, _P, _P]),
     "dlspm_free_host": (None, [_P]),
     "dlspm_sanity_check_csr_host": (_I, [_I, _I, _I, _I, _P, _P, C.c_char_p, C.c_size_t]),
     "dlspm_rand_u64": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
@@ -257,6 +267,17 @@ class Context:
             _dev_ptr(column_indices, torch.int32, "column_indices"), _dev_ptr(Cq, torch.float32, "C"),
             _dev_ptr(Bk, torch.float32, "B"), _dev_ptr(Dv, torch.float32, "D"), _dev_ptr(Eo, torch.float32, "E"),
             _stream_ptr(stream)), "dlspm_fused_sddmm_spmm_f32", self)
+
+    def attention(self, M, K, N, nnz, row_offsets, column_indices, Q, Kmat, V, O, scale=1.0, flags=0,
+                  stream=None) -> None:
+        """O = softmax_rows(scale * pattern .* (Q Kmat^T)) V (flags=ATTN_SOFTMAX) or the scaled chain."""
+        import torch
+
+        _check(self.lib.dlspm_fused_attention_f32(
+            self.handle, M, K, N, nnz, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
+            _dev_ptr(column_indices, torch.int32, "column_indices"), _dev_ptr(Q, torch.float32, "Q"),
+            _dev_ptr(Kmat, torch.float32, "Kmat"), _dev_ptr(V, torch.float32, "V"), _dev_ptr(O, torch.float32, "O"),
+            float(scale), int(flags), _stream_ptr(stream)), "dlspm_fused_attention_f32", self)
 
     def plan_create(self, M, K, nnz, row_offsets, column_indices, stream=None) -> "Plan":
         import torch
@@ -549,6 +570,52 @@ def write_smtx(path: str, M: int, K: int, row_offsets: np.ndarray, column_indice
     nnz = int(column_indices.size)
     _check(lib.dlspm_write_smtx_host(path.encode(), M, K, nnz, _host_ptr(row_offsets, np.int32, "row_offsets"),
                                      _host_ptr(column_indices, np.int32, "column_indices")), "dlspm_write_smtx_host")
+
+
+def _read_with_values(fn_name: str, path: str):
+    lib = load_library()
+    M, K, nnz = _I(), _I(), _I()
+    ro, ci, va = C.POINTER(_I)(), C.POINTER(_I)(), C.POINTER(C.c_float)()
+    _check(getattr(lib, fn_name)(path.encode(), C.byref(M), C.byref(K), C.byref(nnz), C.byref(ro), C.byref(ci),
+                                 C.byref(va)), f"{fn_name}({path})")
+    try:
+        row_offsets = np.ctypeslib.as_array(ro, shape=(M.value + 1,)).copy()
+        cols = np.ctypeslib.as_array(ci, shape=(max(nnz.value, 1),))[: nnz.value].copy()
+        values = np.ctypeslib.as_array(va, shape=(max(nnz.value, 1),))[: nnz.value].copy() if va else None
+    finally:
+        lib.dlspm_free_host(ro)
+        lib.dlspm_free_host(ci)
+        if va:
+            lib.dlspm_free_host(va)
+    return M.value, K.value, nnz.value, row_offsets, cols, values
+
+
+def read_smtx_values(path: str):
+    """Text format with the optional fourth block: (M, K, nnz, row_offsets, column_indices, values or None)."""
+    return _read_with_values("dlspm_read_smtx_values_host", path)
+
+
+def write_smtx_values(path: str, M: int, K: int, row_offsets, column_indices, values) -> None:
+    lib = load_library()
+    nnz = int(column_indices.size)
+    _check(lib.dlspm_write_smtx_values_host(
+        path.encode(), M, K, nnz, _host_ptr(row_offsets, np.int32, "row_offsets"),
+        _host_ptr(column_indices, np.int32, "column_indices"), _host_ptr(values, np.float32, "values")),
+        "dlspm_write_smtx_values_host")
+
+
+def read_csr_cache(path: str):
+    """Binary cache: (M, K, nnz, row_offsets, column_indices, values or None)."""
+    return _read_with_values("dlspm_read_csr_cache_host", path)
+
+
+def write_csr_cache(path: str, M: int, K: int, row_offsets, column_indices, values=None) -> None:
+    lib = load_library()
+    nnz = int(column_indices.size)
+    _check(lib.dlspm_write_csr_cache_host(
+        path.encode(), M, K, nnz, _host_ptr(row_offsets, np.int32, "row_offsets"),
+        _host_ptr(column_indices, np.int32, "column_indices"),
+        _host_ptr(values, np.float32, "values") if values is not None else None), "dlspm_write_csr_cache_host")
 
 
 def sanity_check(M, K, N, nnz, row_offsets, column_indices):

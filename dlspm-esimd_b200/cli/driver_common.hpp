@@ -32,6 +32,10 @@ struct Options {
     bool cold = false;           // also time with L2 flushed between repetitions
     int device = 0;
     std::string csv;
+    bool cache = false;          // from-file drivers: keep a binary copy "<file>.csrbin" beside the text
+    bool attention = false;      // fused driver: scale (and softmax) between the two products
+    bool softmax = false;
+    float scale = 1.f;
 };
 
 inline Options parse(int argc, char **argv)
@@ -48,6 +52,9 @@ inline Options parse(int argc, char **argv)
         else if (a == "--signed") o.signed_values = true;
         else if (a == "--planned") o.planned = true;
         else if (a == "--cold") o.cold = true;
+        else if (a == "--cache") o.cache = true;
+        else if (a == "--softmax") o.attention = o.softmax = true;
+        else if (a == "--scale") { o.attention = true; o.scale = (float)atof(next()); }
         else o.positional.push_back(a);
     }
     return o;
@@ -186,13 +193,15 @@ inline void print_device(dlspm_ctx *ctx)
 // ---- one SpMM case: inputs, optional host check, timed launches, report ------------------------
 // Report lines and CSV columns follow SPMM/spmm-esimd-fromfile.cpp:241-291
 // (CSV: M,N,K,density,gflops,max_diff,opcount).
+// file_values: the values block of the input file if it carried one; generated values otherwise
 inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, const std::vector<int> &ro,
-                         const std::vector<int> &ci)
+                         const std::vector<int> &ci, const std::vector<float> *file_values = nullptr)
 {
     const int nnz = (int)ci.size();
     std::vector<float> vals((size_t)nnz), B((size_t)K * N), C((size_t)M * N, 0.f), Ccpu;
     const int kind = o.signed_values ? 0 : 1;
-    dlspm_gen_dense_host(vals.data(), vals.size(), o.seed, 2, 0, kind);
+    if (file_values && file_values->size() == vals.size()) vals = *file_values;
+    else dlspm_gen_dense_host(vals.data(), vals.size(), o.seed, 2, 0, kind);
     dlspm_gen_dense_host(B.data(), B.size(), o.seed, 10, 0, kind);
     printf("rhs_matrix allocated\n");
     if (o.check) {
@@ -343,6 +352,19 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
         e_gold.resize((size_t)M * N);
         check_sddmm(ro.data(), ci.data(), c.data(), b.data(), a_values.data(), M, N);
         printf("checksum_a_values = %f\n", sqrt(mean_square(a_values.data(), a_values.size())));
+        if (o.attention) {  // weights from the sampled products: scale, then softmax over each row
+            for (int i = 0; i < M; i++) {
+                double top = -INFINITY, sum = 0.0;
+                for (int p = ro[(size_t)i]; p < ro[(size_t)i + 1]; p++) top = std::max(top, (double)a_values[(size_t)p] * o.scale);
+                for (int p = ro[(size_t)i]; p < ro[(size_t)i + 1]; p++) {
+                    const double s = (double)a_values[(size_t)p] * o.scale;
+                    a_values[(size_t)p] = (float)(o.softmax ? exp(s - top) : s);
+                    sum += a_values[(size_t)p];
+                }
+                if (o.softmax)
+                    for (int p = ro[(size_t)i]; p < ro[(size_t)i + 1]; p++) a_values[(size_t)p] = (float)(a_values[(size_t)p] / sum);
+            }
+        }
         check_spmm_f64(a_values.data(), ro.data(), ci.data(), dd.data(), e_gold.data(), M, N);
         printf("checksum_e = %f\n", sqrt(mean_square(e_gold.data(), e_gold.size())));
     }
@@ -354,7 +376,12 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     }
     printf("copy to device completed\n");
     printf("Start kernel execution\n");
-    auto launch = [&]() { return dlspm_fused_sddmm_spmm_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, nullptr); };
+    auto launch = [&]() {
+        if (o.attention)
+            return dlspm_fused_attention_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, o.scale,
+                                             o.softmax ? DLSPM_ATTN_SOFTMAX : 0u, nullptr);
+        return dlspm_fused_sddmm_spmm_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, nullptr);
+    };
     double min_ms = 0, med_ms = 0;
     DRV_TRY(time_launches(launch, o.reps, nullptr, 0, &min_ms, &med_ms));
     printf("MSZ = %d,  NSZ = %d  KSZ = %d  SP = %f\n", M, N, K, (double)nnz / ((double)M * K));
@@ -403,11 +430,24 @@ inline int make_bernoulli(int M, int K, double density, uint64_t seed, std::vect
     return DLSPM_OK;
 }
 
-// Reads a pattern file and validates it, printing what the reference prints on failure.
-inline int load_smtx(const std::string &path, int N, int *M, int *K, std::vector<int> &ro, std::vector<int> &ci)
+// Reads a pattern file and validates it, printing what the reference prints on failure.  With
+// `cache`, a binary copy "<path>.csrbin" is read instead when it exists and is intact, and written
+// after a successful text parse otherwise.  `values` (optional) receives the file's values block,
+// or stays empty if the file has none.
+inline int load_smtx(const std::string &path, int N, int *M, int *K, std::vector<int> &ro, std::vector<int> &ci,
+                     bool cache = false, std::vector<float> *values = nullptr)
 {
     int nnz = 0, *pro = nullptr, *pci = nullptr;
-    int rc = dlspm_read_smtx_host(path.c_str(), M, K, &nnz, &pro, &pci);
+    float *pva = nullptr;
+    const std::string bin = path + ".csrbin";
+    int rc = DLSPM_ERR_IO;
+    bool from_cache = false;
+    if (cache) {
+        rc = dlspm_read_csr_cache_host(bin.c_str(), M, K, &nnz, &pro, &pci, &pva);
+        from_cache = rc == DLSPM_OK;
+        if (from_cache) printf("read %s\n", bin.c_str());
+    }
+    if (!from_cache) rc = dlspm_read_smtx_values_host(path.c_str(), M, K, &nnz, &pro, &pci, &pva);
     if (rc == DLSPM_ERR_IO) {
         printf("Error opening file!\n");
         return rc;
@@ -419,11 +459,24 @@ inline int load_smtx(const std::string &path, int N, int *M, int *K, std::vector
     printf("MSZ: %d, KSZ: %d, NSZ: %d, nnz: %d\n", *M, *K, N, nnz);
     ro.assign(pro, pro + *M + 1);
     ci.assign(pci, pci + nnz);
+    if (values) {
+        values->clear();
+        if (pva) values->assign(pva, pva + nnz);
+    }
     dlspm_free_host(pro);
     dlspm_free_host(pci);
+    dlspm_free_host(pva);
     char why[128];
     rc = dlspm_sanity_check_csr_host(*M, *K, N, nnz, ro.data(), ci.data(), why, sizeof(why));
-    if (rc != DLSPM_OK) printf("%s\n", why);
+    if (rc != DLSPM_OK) {
+        printf("%s\n", why);
+        return rc;
+    }
+    if (cache && !from_cache) {
+        const bool has_values = values && !values->empty();
+        if (dlspm_write_csr_cache_host(bin.c_str(), *M, *K, nnz, ro.data(), ci.data(), has_values ? values->data() : nullptr) == DLSPM_OK)
+            printf("wrote %s\n", bin.c_str());
+    }
     return rc;
 }
 

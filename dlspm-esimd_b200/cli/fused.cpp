@@ -1,7 +1,8 @@
 // Fused SDDMM -> SpMM on a synthetic pattern: ./fused <MSZ> <KSZ> <NSZ> <SP> [options]
 // The reference fixes these four at compile time (-DMSZ -DKSZ -DNSZ -DSP,
 // FUSED/batch-run-fused:29); here they are run-time arguments with the same meaning (SP is the
-// fraction of nonzeros).  --band h adds a band of half-width h around the diagonal.
+// fraction of nonzeros).  --band h adds a band of half-width h around the diagonal; --scale x and
+// --softmax run the sparse-attention form (scaled products, row softmax) instead of the plain chain.
 #include "driver_common.hpp"
 
 int main(int argc, char **argv)
@@ -14,7 +15,7 @@ int main(int argc, char **argv)
     }
     drv::Options o = drv::parse((int)rest.size(), rest.data());
     if (o.positional.size() != 4) {
-        printf("Usage: ./fused <MSZ> <KSZ> <NSZ> <SP> [--band h]\n");
+        printf("Usage: ./fused <MSZ> <KSZ> <NSZ> <SP> [--band h] [--scale x] [--softmax]\n");
         return 0;
     }
     const int M = atoi(o.positional[0].c_str()), K = atoi(o.positional[1].c_str()), N = atoi(o.positional[2].c_str());

@@ -18,7 +18,7 @@ int main(int argc, char **argv)
     drv::print_device(ctx);
     int M = 0, K = 0;
     std::vector<int> ro, ci;
-    int rc = drv::load_smtx(filename, N, &M, &K, ro, ci);
+    int rc = drv::load_smtx(filename, N, &M, &K, ro, ci, o.cache);
     if (rc == DLSPM_OK) rc = drv::run_sddmm_case(ctx, o, M, K, N, ro, ci);
     dlspm_destroy(ctx);
     return rc;

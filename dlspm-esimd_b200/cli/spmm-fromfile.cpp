@@ -1,6 +1,8 @@
 // SpMM from a pattern file: ./spmm-fromfile <filename>.smtx <batchsize> [options]
 // Same command line and report as the reference driver (SPMM/spmm-esimd-fromfile2.cpp:86-95).
-// Options: --reps n, --seed s, --csv file, --no-check, --signed, --planned, --cold, --device d
+// Options: --reps n, --seed s, --csv file, --no-check, --signed, --planned, --cold, --device d,
+// --cache (binary copy of the parsed file beside it).  A file with a values block (fourth block of
+// nnz floats) is multiplied with those values instead of generated ones.
 #include "driver_common.hpp"
 
 int main(int argc, char **argv)
@@ -18,8 +20,9 @@ int main(int argc, char **argv)
     drv::print_device(ctx);
     int M = 0, K = 0;
     std::vector<int> ro, ci;
-    int rc = drv::load_smtx(filename, N, &M, &K, ro, ci);
-    if (rc == DLSPM_OK) rc = drv::run_spmm_case(ctx, o, M, K, N, ro, ci);
+    std::vector<float> values;  // taken from the file when it carries a values block
+    int rc = drv::load_smtx(filename, N, &M, &K, ro, ci, o.cache, &values);
+    if (rc == DLSPM_OK) rc = drv::run_spmm_case(ctx, o, M, K, N, ro, ci, values.empty() ? nullptr : &values);
     dlspm_destroy(ctx);
     return rc;
 }

@@ -7,6 +7,9 @@
 
 #include "../../include/dlspm.h"
 
+// staging slots of the pipelined host-buffer calls (copy in, launch, copy out overlap across slots)
+constexpr int kPipeSlots = 4;
+
 struct dlspm_ctx {
     int device;
     int sm_count;
@@ -25,7 +28,7 @@ struct dlspm_ctx {
     cudaStream_t stream;  // private stream of the *_host entry points (compute)
     // copy streams and events of the pipelined host-buffer batch (created on first use)
     cudaStream_t h2d_stream, d2h_stream;
-    cudaEvent_t ev_h2d[2], ev_kernel[2], ev_d2h[2];
+    cudaEvent_t ev_h2d[kPipeSlots], ev_kernel[kPipeSlots], ev_d2h[kPipeSlots];
     int pipeline_ready;
     void *pinned;  // pinned host memory for the launch tables of the pipelined batch
     size_t pinned_bytes;

@@ -80,7 +80,7 @@ extern "C" int dlspm_destroy(dlspm_ctx *ctx)
     if (ctx->pipeline_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < kPipeSlots; i++) {
             cudaEventDestroy(ctx->ev_h2d[i]);
             cudaEventDestroy(ctx->ev_kernel[i]);
             cudaEventDestroy(ctx->ev_d2h[i]);

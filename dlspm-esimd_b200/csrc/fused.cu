@@ -8,6 +8,12 @@
 // the 32/G group partial sums are added with shuffles and one group stores the row of E.
 // The reference keeps a 32-score vector per row in registers in the same way
 // (FUSED/fused-esimd_cb.cpp:130-154); it needs a zeroed E for empty rows, this kernel writes them.
+//
+// The same kernels carry two optional steps between the two products (template parameter MODE):
+// a scale factor on the sampled products, and a softmax over the stored entries of each row
+// (sparse attention).  The softmax is the streaming form: a running maximum and a running sum per
+// row, and the partial output row is rescaled whenever the maximum grows, so a row is still read
+// once and nothing is written besides the output row.
 #include "common.cuh"
 #include "sddmm_device.cuh"
 
@@ -17,11 +23,26 @@ namespace {
 
 constexpr int kWarps = 8;
 
-template <int G, int R>
+constexpr int kPlain = 0, kScaled = 1, kSoftmax = 2;
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    return v;
+}
+
+template <int G, int R, int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
-                  float *__restrict__ e, int M, int chunks)
+                  float *__restrict__ e, int M, int chunks, float scale)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarps + warp;
@@ -39,11 +60,30 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
     // column indices of the next pass are fetched one pass ahead
     int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
+    [[maybe_unused]] float run_max = -INFINITY, run_sum = 0.f;
     for (int base = start; base < end; base += 32) {
         const int p = base + lane;
         const int col = col_next;
         col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
-        const float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
+        float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
+        if constexpr (MODE == kScaled) score *= scale;
+        if constexpr (MODE == kSoftmax) {
+            // streaming softmax: weights relative to the running maximum; the partial row and the
+            // running sum are rescaled when the maximum grows
+            const float x = col >= 0 ? score * scale : -INFINITY;
+            const float m_new = fmaxf(run_max, warp_max(x));  // finite: a pass has a stored entry
+            const float corr = expf(run_max - m_new);         // 0 on the first pass
+            score = col >= 0 ? expf(x - m_new) : 0.f;
+            run_sum = run_sum * corr + warp_sum(score);
+            run_max = m_new;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                acc[r].x *= corr;
+                acc[r].y *= corr;
+                acc[r].z *= corr;
+                acc[r].w *= corr;
+            }
+        }
 #pragma unroll
         for (int k = 0; k < G; k++) {
             const int src = g * G + k;
@@ -76,6 +116,16 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
             acc[r].w += __shfl_xor_sync(0xffffffffu, acc[r].w, s);
         }
     }
+    if constexpr (MODE == kSoftmax) {
+        const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;  // empty row: zeros
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            acc[r].x *= inv;
+            acc[r].y *= inv;
+            acc[r].z *= inv;
+            acc[r].w *= inv;
+        }
+    }
     if (g == 0) {
         float4 *e4 = reinterpret_cast<float4 *>(e) + (size_t)row * (size_t)chunks;
 #pragma unroll
@@ -88,10 +138,11 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
 
 // Any N and alignment.  The output row is produced in slabs of 128 columns per pass over the row's
 // nonzeros; scores are recomputed for every slab, so nothing is spilled to memory.
+template <int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                      const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
-                     float *__restrict__ e, int M, int N)
+                     float *__restrict__ e, int M, int N, float scale)
 {
     constexpr int U = 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,6 +154,7 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
         float acc[U];
 #pragma unroll
         for (int u = 0; u < U; u++) acc[u] = 0.f;
+        [[maybe_unused]] float run_max = -INFINITY, run_sum = 0.f;
         for (int base = start; base < end; base += 32) {
             const int p = base + lane;
             const int col = p < end ? __ldg(cols + p) : 0;
@@ -114,6 +166,17 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
                 for (int l = lane; l < N; l += 32) s = fmaf(__ldg(crow + l), __ldg(brow + l), s);
 #pragma unroll
                 for (int w = 16; w >= 1; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+                if constexpr (MODE == kScaled) s *= scale;
+                if constexpr (MODE == kSoftmax) {
+                    const float x = s * scale;
+                    const float m_new = fmaxf(run_max, x);
+                    const float corr = expf(run_max - m_new);
+                    s = expf(x - m_new);
+                    run_sum = run_sum * corr + s;
+                    run_max = m_new;
+#pragma unroll
+                    for (int u = 0; u < U; u++) acc[u] *= corr;
+                }
                 const float *drow = d + (size_t)cc * (size_t)N;
 #pragma unroll
                 for (int u = 0; u < U; u++) {
@@ -122,27 +185,27 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
                 }
             }
         }
+        [[maybe_unused]] const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int j = n0 + u * 32 + lane;
+            if constexpr (MODE == kSoftmax) acc[u] *= inv;
             if (j < N) e[(size_t)row * (size_t)N + j] = acc[u];
         }
     }
 }
 
-template <int G, int R>
+template <int G, int R, int MODE>
 void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
-                 int M, int chunks, cudaStream_t st)
+                 int M, int chunks, float scale, cudaStream_t st)
 {
-    fused_rows_kernel<G, R><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks);
+    fused_rows_kernel<G, R, MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
 }
 
-}  // namespace
-
-extern "C" int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
-                                          const int *row_offsets, const int *column_indices,
-                                          const float *C, const float *B, const float *D, float *E,
-                                          void *stream)
+template <int MODE>
+int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                 const int *column_indices, const float *C, const float *B, const float *D, float *E,
+                 float scale, void *stream)
 {
     if (!ctx || M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
     if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
@@ -157,15 +220,37 @@ extern "C" int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, i
     int G = 0, R = 0;
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
-        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
-        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
-        else launch_fast<32, 8>(row_offsets, column_indices, C, B, D, E, M, chunks, st);
+        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
     } else {
-        fused_generic_kernel<<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N);
+        fused_generic_kernel<MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N, scale);
     }
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                                          const int *row_offsets, const int *column_indices,
+                                          const float *C, const float *B, const float *D, float *E,
+                                          void *stream)
+{
+    return fused_launch<kPlain>(ctx, M, K, N, nnz, row_offsets, column_indices, C, B, D, E, 1.f, stream);
+}
+
+extern "C" int dlspm_fused_attention_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                                         const int *row_offsets, const int *column_indices,
+                                         const float *Q, const float *Kmat, const float *V, float *O,
+                                         float scale, unsigned flags, void *stream)
+{
+    if (flags & ~(unsigned)DLSPM_ATTN_SOFTMAX) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (!(scale == scale) || scale - scale != 0.f) return DLSPM_ERR_INVALID_ARGUMENT;  // NaN or infinite
+    if (flags & DLSPM_ATTN_SOFTMAX)
+        return fused_launch<kSoftmax>(ctx, M, K, N, nnz, row_offsets, column_indices, Q, Kmat, V, O, scale, stream);
+    return fused_launch<kScaled>(ctx, M, K, N, nnz, row_offsets, column_indices, Q, Kmat, V, O, scale, stream);
 }

@@ -129,10 +129,12 @@ extern "C" int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int
     return DLSPM_OK;
 }
 
-// Batched SpMM with host pointers, pipelined: the batch is cut into pieces of at most 256 MiB of
-// device copies; two staging buffers alternate, and three streams overlap the host-to-device copy
-// of piece i+1, the grouped launch of piece i and the device-to-host copy of piece i-1 (PCIe is
-// full duplex, so the slower of the two copy directions bounds the call, not their sum).
+// Batched SpMM with host pointers, pipelined: the batch is cut into pieces of at most 128 MiB of
+// device copies; kPipeSlots staging buffers rotate, and three streams overlap the host-to-device
+// copies of the next pieces, the grouped launch of the current one and the device-to-host copies
+// of the previous ones (PCIe is full duplex, so the slower of the two copy directions bounds the
+// call, not their sum).  More than two slots keep the inbound copies running while a finished
+// piece still waits for its turn on the outbound stream.
 namespace {
 
 int pipeline_init(dlspm_ctx *ctx)
@@ -140,7 +142,7 @@ int pipeline_init(dlspm_ctx *ctx)
     if (ctx->pipeline_ready) return DLSPM_OK;
     DLSPM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
     DLSPM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < kPipeSlots; i++) {
         DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_h2d[i], cudaEventDisableTiming));
         DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_kernel[i], cudaEventDisableTiming));
         DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_d2h[i], cudaEventDisableTiming));
@@ -156,7 +158,7 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
     if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
-    const size_t budget = (size_t)256 << 20;
+    const size_t budget = (size_t)128 << 20;
     auto need = [](const dlspm_problem &q) {
         return padded(4 * ((size_t)q.M + 1)) + 2 * padded(4 * (size_t)q.nnz) + padded(4 * (size_t)q.K * q.N) +
                padded(4 * (size_t)q.M * q.N);
@@ -186,31 +188,31 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
         first = last;
     }
     const size_t slot = padded(max_piece) + padded(max_tables);
-    rc = dlspm_stage_reserve(ctx, 2 * slot + 256);
+    rc = dlspm_stage_reserve(ctx, (size_t)kPipeSlots * slot + 256);
     if (rc) return rc;
     // the launch tables travel from pinned memory: a copy from pageable memory would synchronise
     // the compute stream with the host and serialise the pipeline
-    if (ctx->pinned_bytes < 2 * padded(max_tables)) {
+    if (ctx->pinned_bytes < (size_t)kPipeSlots * padded(max_tables)) {
         if (ctx->pinned) cudaFreeHost(ctx->pinned);
         ctx->pinned = nullptr;
         ctx->pinned_bytes = 0;
-        cudaError_t perr = cudaMallocHost(&ctx->pinned, 2 * padded(max_tables));
+        cudaError_t perr = cudaMallocHost(&ctx->pinned, (size_t)kPipeSlots * padded(max_tables));
         if (perr != cudaSuccess) {
             dlspm_cuda_fail(ctx, perr, "cudaMallocHost(tables)");
             return DLSPM_ERR_NOMEM;
         }
-        ctx->pinned_bytes = 2 * padded(max_tables);
+        ctx->pinned_bytes = (size_t)kPipeSlots * padded(max_tables);
     }
     cudaStream_t h2d = ctx->h2d_stream, run = ctx->stream, d2h = ctx->d2h_stream;
-    std::vector<dlspm_problem> dev[2];
+    std::vector<dlspm_problem> dev[kPipeSlots];
     int first = 0;
     for (size_t pi = 0; pi < piece_end.size(); pi++) {
         const int last = piece_end[pi];
-        const int b = (int)(pi & 1);
+        const int b = (int)(pi % kPipeSlots);
         char *base = (char *)ctx->stage + (size_t)b * slot;
-        // the slot is free once the results of the piece that used it two rounds ago have left;
-        // its pinned table may be rewritten once that piece's launch has finished
-        if (pi >= 2) {
+        // the slot is free once the results of the piece that used it last have left; its pinned
+        // table may be rewritten once that piece's launch has finished
+        if (pi >= (size_t)kPipeSlots) {
             DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(h2d, ctx->ev_d2h[b], 0));
             DLSPM_CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev_kernel[b]));
         }

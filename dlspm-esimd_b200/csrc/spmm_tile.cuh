@@ -96,13 +96,24 @@ __device__ __forceinline__ void cp_async_4(void *dst, const void *src)
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Issues the B chunk starting at row k0 into stage s (called by warp 0 only).  Rows past the end of
-// B are never read: no mask bit can point at them.
+// B (last chunk when K is not a multiple of 32) are written as zeros: the masked inner loop never
+// reads them, but the zero-filled variant multiplies every row of the chunk, and stale shared
+// memory there could hold a NaN.
 __device__ __forceinline__ void tile_load_b(TileSmem &sm, const TileProblem &p, int s, int k0, int n0, int lane)
 {
     const int cols = min(kTileN, p.N - n0);
     const unsigned row_bytes = (unsigned)cols * 4u;
     const int rows = min(kTileK, p.K - k0);
+    if (rows < kTileK) {
+        for (int r = rows; r < kTileK; r++)
+            for (int c = lane * 4; c < kTileN; c += 128)
+                *reinterpret_cast<float4 *>(&sm.Bs[s][r][c]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        fence_async_smem();  // these generic-proxy writes precede later bulk copies into the same rows
+        __syncwarp();
+    }
     if (lane == 0) mbar_expect_tx(&sm.full[s], row_bytes * (unsigned)rows);
     __syncwarp();
     if (lane < rows)

@@ -120,6 +120,21 @@ int dlspm_fused_sddmm_spmm_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
                                const float *C, const float *B, const float *D, float *E,
                                void *stream);
 
+/* Sparse attention around the fused kernel: O[i, :] = sum_p w_p * V[column_indices[p], :] over the
+ * stored entries p of row i, with s_p = scale * dot(Q[i, :], Kmat[column_indices[p], :]) and
+ *   flags = 0:                   w_p = s_p              (the fused chain with a scale factor)
+ *   flags = DLSPM_ATTN_SOFTMAX:  w_p = exp(s_p - max_p s_p) / sum_p exp(s_p - max_p s_p)
+ * The weights never reach memory; rows without stored entries give zeros.  Q and O are M x N,
+ * Kmat and V are K x N; scale must be finite.  The reference has no counterpart of the two extra
+ * steps (its fused chain is FUSED/fused-esimd_cb.cpp:100-189, which this call reproduces for
+ * flags = 0, scale = 1); the checker for them is a double-precision restatement of the formulas
+ * above, so their parity is not pinned to reference code. */
+#define DLSPM_ATTN_SOFTMAX 1u
+int dlspm_fused_attention_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                              const int *row_offsets, const int *column_indices,
+                              const float *Q, const float *Kmat, const float *V, float *O,
+                              float scale, unsigned flags, void *stream);
+
 /* ---- plans ------------------------------------------------------------------------ */
 
 /* Bins the rows of one pattern by length so that warps of one thread block get rows of similar
@@ -207,6 +222,25 @@ int dlspm_read_smtx_host(const char *path, int *M, int *K, int *nnz, int **row_o
 /* Writes the same text format (used by tests and by the drivers' --dump option). */
 int dlspm_write_smtx_host(const char *path, int M, int K, int nnz, const int *row_offsets,
                           const int *column_indices);
+/* The text format with values: a fourth block of nnz decimal floats ("%.9g", exact for fp32)
+ * after the column indices.  The reference's format carries no values (its drivers fill them with
+ * rand(), SPMM/spmm-esimd-fromfile.cpp:140-149) and its reader stops after the indices, so such a
+ * file is still a valid pattern file for it.  On reading, *values is NULL when the file has no
+ * fourth block. */
+int dlspm_read_smtx_values_host(const char *path, int *M, int *K, int *nnz, int **row_offsets,
+                                int **column_indices, float **values);
+int dlspm_write_smtx_values_host(const char *path, int M, int K, int nnz, const int *row_offsets,
+                                 const int *column_indices, const float *values);
+/* Binary cache of a parsed matrix, so that large inputs are not re-parsed from text: 48-byte
+ * little-endian header (magic "DLSPMCSR", version, flags, M, K, nnz, checksum, payload size),
+ * then row_offsets, column_indices and, if values != NULL, values, each padded to 8 bytes.
+ * Reading verifies magic, version, sizes against the file length and the checksum
+ * (DLSPM_ERR_FORMAT otherwise); *values is NULL when the file carries none.  No reference
+ * counterpart. */
+int dlspm_write_csr_cache_host(const char *path, int M, int K, int nnz, const int *row_offsets,
+                               const int *column_indices, const float *values);
+int dlspm_read_csr_cache_host(const char *path, int *M, int *K, int *nnz, int **row_offsets,
+                              int **column_indices, float **values);
 void dlspm_free_host(void *p);
 
 /* The reference's SanityCheck (SPMM/spmm-esimd-fromfile.cpp:36-61): nnz <= M*K,

@@ -43,6 +43,7 @@ def lib() -> C.CDLL:
         l.oracle_sddmm_mt.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I]
         l.oracle_fused.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I]
         l.oracle_fused_mt.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]
+        l.oracle_attention.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, C.c_float, _I]
         l.oracle_fused_order.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I]
         l.oracle_spmm_scale.argtypes = [_P, _P, _P, _P, _P, _I, _I]
         l.oracle_sddmm_scale.argtypes = [_P, _P, _P, _P, _P, _I, _I]
@@ -119,6 +120,15 @@ def fused(row_offsets, cols, c, b, d, M, N, threads: int = 1):
     else:
         lib().oracle_fused(_p(row_offsets), _p(cols), _p(c), _p(b), _p(d), _p(e), _p(a), M, N)
     return e, a[: cols.size]
+
+
+def attention(row_offsets, cols, q, k, v, M, N, scale: float, softmax: bool):
+    """Double-precision sparse attention (scale, optional row softmax); returns (O, magnitude)."""
+    o = np.empty((M, N), dtype=np.float32)
+    mag = np.empty((M, N), dtype=np.float32)
+    lib().oracle_attention(_p(row_offsets), _p(cols), _p(q), _p(k), _p(v), _p(o), _p(mag), M, N,
+                           C.c_float(scale), int(bool(softmax)))
+    return o, mag
 
 
 def fused_order(row_offsets, cols, c, b, d, M, N) -> np.ndarray:

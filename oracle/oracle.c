@@ -212,6 +212,52 @@ void oracle_fused_mt(const int *row_offsets, const int *column_indices, const fl
     oracle_parallel_rows(spmm_f64acc_rows, &g, M, threads);
 }
 
+/* -------- sparse attention: scale and row softmax between Sddmm and Spmm -----------------------
+ * No reference code exists for these two steps (the reference's chain is FUSED/fused.cpp:47-89);
+ * this is the textbook two-pass form in double precision, so its parity is unpinned.
+ *   s_p = scale * dot(q_i, k_col_p);  softmax: w_p = exp(s_p - max) / sum exp(s_p - max), else w_p = s_p
+ *   o[i, :] = sum_p w_p * v[col_p, :]
+ * mag (optional) receives sum_p |w_p| * |v[col_p, j]| for the tolerance test. */
+void oracle_attention(const int *row_offsets, const int *column_indices, const float *q,
+                      const float *k, const float *v, float *o, float *mag, int M, int N, float scale,
+                      int softmax)
+{
+    int longest = 1;
+    for (int i = 0; i < M; i++)
+        if (row_offsets[i + 1] - row_offsets[i] > longest) longest = row_offsets[i + 1] - row_offsets[i];
+    double *w = (double *)malloc(sizeof(double) * (size_t)longest);
+    for (int i = 0; i < M; i++) {
+        const int start = row_offsets[i], len = row_offsets[i + 1] - start;
+        double top = -INFINITY;
+        for (int p = 0; p < len; p++) {
+            const int col = column_indices[start + p];
+            double acc = 0.0;
+            for (int l = 0; l < N; l++) acc += (double)q[(size_t)i * N + l] * (double)k[(size_t)col * N + l];
+            w[p] = acc * (double)scale;
+            if (w[p] > top) top = w[p];
+        }
+        if (softmax) {
+            double sum = 0.0;
+            for (int p = 0; p < len; p++) {
+                w[p] = exp(w[p] - top);
+                sum += w[p];
+            }
+            for (int p = 0; p < len; p++) w[p] /= sum;
+        }
+        for (int j = 0; j < N; j++) {
+            double acc = 0.0, m = 0.0;
+            for (int p = 0; p < len; p++) {
+                const double x = (double)v[(size_t)column_indices[start + p] * N + j];
+                acc += w[p] * x;
+                m += fabs(w[p]) * fabs(x);
+            }
+            o[(size_t)i * N + j] = (float)acc;
+            if (mag) mag[(size_t)i * N + j] = (float)m;
+        }
+    }
+    free(w);
+}
+
 /* -------- the fp32 emulation of the fused kernel's order: FUSED/fused.cpp:93-216 ------------
  * Per row: products c[i,m]*b[col,m] rounded to fp32, summed left to right into element 0,
  * then e_row += score * d_row in CSR order.  The 32-wide chunking of the original does not

@@ -284,6 +284,47 @@ def test_tiled_kernel_matches_gather_and_oracle(pkg, oracle, ctx, dev):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
+def test_zero_filled_tiles_do_not_see_stale_rows(pkg, oracle, ctx, dev):
+    """A block of the zero-filled variant that first stages a B full of infinities and then a tile
+    whose K ends inside a 32-row chunk must not multiply the leftovers of the first one."""
+    import torch
+
+    Mh, Kh, N = 64, 64, 256
+    roh, cih = csr_rowlen_normal(pkg, Mh, Kh, 0.5, 901)
+    hot = [to_dev(a, dev) for a in (pkg.gen_dense_host(int(cih.size), 901, 2), roh, cih)]
+    hotB = torch.full((Kh * N,), float("inf"), device=dev)
+    Mc, Kc = 64, 33
+    roc, cic = csr_rowlen_normal(pkg, Mc, Kc, 0.5, 902)
+    valsc, Bc = pkg.gen_dense_host(int(cic.size), 902, 2), dense(pkg, Kc, N, 902, 10)
+    cold = [to_dev(a, dev) for a in (valsc, roc, cic, Bc)]
+    count = 1200  # several tiles per resident block
+    ctx.set_option(pkg.OPT_SPMM_KERNEL, pkg.SPMM_KERNEL_TILED_DENSE)
+    try:
+        arr = pkg.ProblemArray(count)
+        outs = torch.full((count, Mc * N), float("nan"), device=dev)
+        for i in range(count):
+            if i % 2 == 0:
+                arr.set(i, Mh, Kh, N, int(cih.size), hot[0], hot[1], hot[2], hotB, outs[i])
+            else:
+                arr.set(i, Mc, Kc, N, int(cic.size), cold[0], cold[1], cold[2], cold[3], outs[i])
+        batch = ctx.batch_create(arr)
+        batch.launch()
+        torch.cuda.synchronize()
+        info = batch.info(check_device=True)
+        batch.close()
+    finally:
+        ctx.set_option(pkg.OPT_SPMM_KERNEL, pkg.SPMM_KERNEL_AUTO)
+    assert info[1] == count and info[2] == 0
+    got = outs[1::2].cpu().numpy()
+    ref = oracle.spmm(valsc, roc, cic, Bc, Mc, N)
+    scale = oracle.spmm_scale(valsc, roc, cic, Bc, Mc, N)
+    assert np.isfinite(got).all()
+    for row in (0, got.shape[0] // 2, got.shape[0] - 1):
+        bad, worst = oracle.violations(ref, got[row].reshape(Mc, N), scale, TOL)
+        assert bad == 0, worst
+    assert (got == got[0]).all()
+
+
 def test_tiled_kernel_strict_mode_is_bit_exact(pkg, oracle, ctx, dev):
     probs = tiled_cases(pkg)[:4]
     ctx.set_option(pkg.OPT_STRICT_FP32, 1)

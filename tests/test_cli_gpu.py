@@ -43,6 +43,28 @@ def test_spmm_fromfile(pkg, tmp_path):
     assert "cold-L2 median ms" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
 
 
+def test_spmm_fromfile_cache_and_file_values(pkg, tmp_path):
+    """--cache writes a binary copy on the first run and reads it on the second; a values block in
+    the file replaces the generated values (same report either way)."""
+    ro, ci = pkg.gen_bernoulli_csr_host(200, 150, 0.1, 8)
+    vals = pkg.gen_dense_host(int(ci.size), 8, 2)
+    smtx = str(tmp_path / "v.smtx")
+    pkg.write_smtx_values(smtx, 200, 150, ro, ci, vals)
+    first = _run(pkg, "spmm-fromfile", smtx, 32, "--cache")
+    assert f"wrote {smtx}.csrbin" in first and os.path.exists(smtx + ".csrbin")
+    second = _run(pkg, "spmm-fromfile", smtx, 32, "--cache")
+    assert f"read {smtx}.csrbin" in second
+    plain = str(tmp_path / "p.smtx")
+    pkg.write_smtx(plain, 200, 150, ro, ci)
+    generated = _run(pkg, "spmm-fromfile", plain, 32)
+    sums = [_value(o, r"checksum_gpu = ([0-9.e+-]+)") for o in (first, second, generated)]
+    assert sums[0] == sums[1] and sums[0] != sums[2]
+    for o in (first, second):
+        assert _value(o, r"max_diff = ([0-9.e+-]+)") < 1e-4
+    M, K, nnz, ro2, ci2, v2 = pkg.read_csr_cache(smtx + ".csrbin")
+    assert np.array_equal(ci2, ci) and np.array_equal(v2.view(np.uint32), vals.view(np.uint32))
+
+
 def test_spmm_fromfile_errors(pkg, tmp_path):
     out = _run(pkg, "spmm-fromfile")
     assert "Usage: ./app <filename>.smtx <batchsize>" in out
@@ -69,6 +91,9 @@ def test_sddmm_fromfile_and_fused(pkg, tmp_path):
     assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
     out = _run(pkg, "fused", 256, 256, 64, 0.05, "--band", 8)
     assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
+    out = _run(pkg, "fused", 256, 256, 64, 0.05, "--band", 8, "--signed", "--scale", 2000, "--softmax")
+    assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
+    assert _value(out, r"checksum_e using gpu = ([0-9.e+-]+)") > 0
 
 
 def test_sweep_drivers_single_case(pkg):

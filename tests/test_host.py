@@ -94,6 +94,74 @@ def test_smtx_missing_file(pkg, tmp_path):
     assert e.value.status == pkg.ERR_IO
 
 
+def test_smtx_with_values_round_trip(pkg, oracle, tmp_path):
+    ro, ci = pkg.gen_bernoulli_csr_host(29, 41, 0.3, 5)
+    vals = pkg.gen_dense_host(int(ci.size), 5, 2, kind=pkg.KIND_NORMAL)
+    vals[:3] = [np.float32(1e-38), np.float32(-3.4e38), np.float32(1) / np.float32(3)]
+    p = str(tmp_path / "v.smtx")
+    pkg.write_smtx_values(p, 29, 41, ro, ci, vals)
+    M, K, nnz, ro2, ci2, v2 = pkg.read_smtx_values(p)
+    assert (M, K, nnz) == (29, 41, ci.size) and np.array_equal(ro, ro2) and np.array_equal(ci, ci2)
+    assert np.array_equal(vals.view(np.uint32), v2.view(np.uint32))  # nine digits: every bit comes back
+    # the plain readers (this library's and the fscanf one) take it as a pattern file
+    assert np.array_equal(pkg.read_smtx(p)[4], ci)
+    assert np.array_equal(oracle.read_smtx(p)[4], ci)
+    # a plain file has no values
+    q = str(tmp_path / "plain.smtx")
+    pkg.write_smtx(q, 29, 41, ro, ci)
+    assert pkg.read_smtx_values(q)[5] is None
+    # a values block that is too short or not numeric is a format error
+    for tail in ("0.5 0.25\n", "0.5 x\n"):
+        bad = tmp_path / "short.smtx"
+        bad.write_text("2, 2, 3\n0 1 3\n0 0 1\n" + tail)
+        with pytest.raises(pkg.DlspmError) as e:
+            pkg.read_smtx_values(str(bad))
+        assert e.value.status == pkg.ERR_FORMAT
+
+
+@pytest.mark.parametrize("with_values", [False, True])
+def test_csr_cache_round_trip_and_corruption(pkg, tmp_path, with_values):
+    M, K = 61, 47
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.15, 6)
+    vals = pkg.gen_dense_host(int(ci.size), 6, 2) if with_values else None
+    p = str(tmp_path / "m.csrbin")
+    pkg.write_csr_cache(p, M, K, ro, ci, vals)
+    M2, K2, nnz2, ro2, ci2, v2 = pkg.read_csr_cache(p)
+    assert (M2, K2, nnz2) == (M, K, ci.size) and np.array_equal(ro, ro2) and np.array_equal(ci, ci2)
+    assert (v2 is None) == (vals is None)
+    if with_values:
+        assert np.array_equal(vals.view(np.uint32), v2.view(np.uint32))
+    blob = bytearray(open(p, "rb").read())
+    assert len(blob) % 8 == 0 and blob[:8] == b"DLSPMCSR"
+
+    def expect_format_error(data):
+        bad = str(tmp_path / "bad.csrbin")
+        open(bad, "wb").write(bytes(data))
+        with pytest.raises(pkg.DlspmError) as e:
+            pkg.read_csr_cache(bad)
+        assert e.value.status == pkg.ERR_FORMAT
+
+    flipped = bytearray(blob)
+    flipped[48 + 4 * 7] ^= 0x10                      # one bit of a row offset
+    expect_format_error(flipped)
+    expect_format_error(blob[:-8])                   # truncated
+    expect_format_error(blob + b"\0" * 8)            # trailing bytes
+    expect_format_error(b"NOTACSR!" + bytes(blob[8:]))
+    huge = bytearray(blob)
+    huge[24:28] = (2**31 - 1).to_bytes(4, "little")  # nnz far beyond the file: rejected before allocation
+    expect_format_error(huge)
+    with pytest.raises(pkg.DlspmError) as e:
+        pkg.read_csr_cache(str(tmp_path / "absent.csrbin"))
+    assert e.value.status == pkg.ERR_IO
+
+
+def test_csr_cache_empty_matrix(pkg, tmp_path):
+    p = str(tmp_path / "e.csrbin")
+    pkg.write_csr_cache(p, 3, 5, np.zeros(4, dtype=np.int32), np.zeros(0, dtype=np.int32))
+    M, K, nnz, ro, ci, v = pkg.read_csr_cache(p)
+    assert (M, K, nnz) == (3, 5, 0) and ro.tolist() == [0, 0, 0, 0] and ci.size == 0 and v is None
+
+
 def test_reader_matches_fscanf_reader_on_dataset_files(pkg, oracle):
     """Bit-exact index handling on real pattern files, where the dataset checkout is present."""
     root = os.path.join(os.environ.get("DLSPM_REFERENCE_DIR", "/root/reference"), "dlmc")

@@ -119,6 +119,34 @@ def test_oracle_spmm_matches_numpy_float64(pkg, oracle):
     np.testing.assert_allclose(e, S @ rhs.astype(np.float64), rtol=1e-5, atol=1e-5)
 
 
+def test_oracle_attention_matches_numpy_float64(pkg, oracle):
+    """The scale / row-softmax steps have no reference code; the restatement is checked against a
+    dense float64 masked softmax."""
+    M, K, N = 33, 41, 12
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.25, 8)
+    ro = ro.copy()
+    q = pkg.gen_dense_host(M * N, 8, 11).reshape(M, N).astype(np.float64)
+    k = pkg.gen_dense_host(K * N, 8, 12).reshape(K, N).astype(np.float64)
+    v = pkg.gen_dense_host(K * N, 8, 13).reshape(K, N).astype(np.float64)
+    scores = 0.7 * (q @ k.T)
+    mask = np.zeros((M, K), dtype=bool)
+    for i in range(M):
+        mask[i, ci[ro[i]:ro[i + 1]]] = True
+    want_scaled = np.where(mask, scores, 0.0) @ v
+    e = np.where(mask, np.exp(scores - np.where(mask, scores, -np.inf).max(axis=1, keepdims=True, initial=-1e300)), 0.0)
+    denom = e.sum(axis=1, keepdims=True)
+    want_soft = np.divide(e, denom, out=np.zeros_like(e), where=denom > 0) @ v
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    got, mag = oracle.attention(ro, ci, f32(q), f32(k), f32(v), M, N, 0.7, False)
+    np.testing.assert_allclose(got, want_scaled, rtol=1e-5, atol=1e-5)
+    got, mag = oracle.attention(ro, ci, f32(q), f32(k), f32(v), M, N, 0.7, True)
+    np.testing.assert_allclose(got, want_soft, rtol=1e-5, atol=1e-5)
+    assert (mag + 1e-6 >= np.abs(got)).all()
+    for i in range(M):
+        if ro[i] == ro[i + 1]:
+            assert (got[i] == 0).all()
+
+
 def test_violation_counter(oracle):
     ref = np.array([1.0, 0.0, 2.0, 0.0], dtype=np.float32)
     out = np.array([1.00005, 1e-6, 2.1, 0.0], dtype=np.float32)
