@@ -61,6 +61,7 @@ _SIGNATURES = {
     "dlspm_spmm_csr_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "dlspm_spmm_csr_f32_planned": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P]),
     "dlspm_sddmm_csr_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "dlspm_sddmm_csr_masked_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "dlspm_fused_sddmm_spmm_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "dlspm_fused_attention_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, C.c_float, C.c_uint, _P]),
     "dlspm_plan_create": (_I, [_P, _I, _I, _I, _P, _P, _P, C.POINTER(_P)]),
@@ -258,6 +259,17 @@ class Context:
             _dev_ptr(column_indices, torch.int32, "column_indices"), _dev_ptr(lhs, torch.float32, "lhs"),
             _dev_ptr(rhs, torch.float32, "rhs"), _dev_ptr(out, torch.float32, "out"), _stream_ptr(stream)),
             "dlspm_sddmm_csr_f32", self)
+
+    def sddmm_masked(self, M, K, N, nnz, row_offsets, column_indices, mask_values, lhs, rhs, out, stream=None) -> None:
+        """out[p] = mask_values[p] * dot(lhs[i], rhs[col_p]); mask_values None means 1."""
+        import torch
+
+        _check(self.lib.dlspm_sddmm_csr_masked_f32(
+            self.handle, M, K, N, nnz, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
+            _dev_ptr(column_indices, torch.int32, "column_indices"),
+            _dev_ptr(mask_values, torch.float32, "mask_values") if mask_values is not None else None,
+            _dev_ptr(lhs, torch.float32, "lhs"), _dev_ptr(rhs, torch.float32, "rhs"),
+            _dev_ptr(out, torch.float32, "out"), _stream_ptr(stream)), "dlspm_sddmm_csr_masked_f32", self)
 
     def fused(self, M, K, N, nnz, row_offsets, column_indices, Cq, Bk, Dv, Eo, stream=None) -> None:
         import torch

@@ -15,11 +15,12 @@ namespace {
 
 constexpr int kWarps = 8;
 
+// `mask` (may be null) holds one factor per stored entry: out[p] = mask[p] * dot.
 template <int G, int R>
 __global__ void __launch_bounds__(kWarps * 32)
 sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
-                  int M, int chunks)
+                  int M, int chunks, const float *__restrict__ mask)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarps + warp;
@@ -38,7 +39,7 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
         const int col = col_next;
         col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
         const float r = sddmm_pass<G, R>(a, rhs4, chunks, col, g, t);
-        if (p < end) out[p] = r;
+        if (p < end) out[p] = mask ? __ldg(mask + p) * r : r;
     }
 }
 
@@ -49,7 +50,7 @@ template <int R>
 __global__ void __launch_bounds__(kWarps * 32)
 sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                        const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
-                       int M, int chunks)
+                       int M, int chunks, const float *__restrict__ mask)
 {
     constexpr int G = 32, kSeg = G * R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,7 +74,7 @@ sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restric
             sddmm_accumulate<G, R>(part, a, rhs4 + seg, len, chunks, col, 0, lane);
         }
         group_transpose_reduce<G>(part, lane);
-        if (p < end) out[p] = part[0];
+        if (p < end) out[p] = mask ? __ldg(mask + p) * part[0] : part[0];
     }
 }
 
@@ -82,7 +83,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kWarps * 32)
 sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                      const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
-                     int M, int N)
+                     int M, int N, const float *__restrict__ mask)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarps + warp;
@@ -115,22 +116,20 @@ sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
             for (int s = 16; s >= 1; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
             if (lane == k) mine = acc;
         }
-        if (p < end) out[p] = mine;
+        if (p < end) out[p] = mask ? __ldg(mask + p) * mine : mine;
     }
 }
 
 template <int G, int R>
 void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M,
-                 int chunks, cudaStream_t st)
+                 int chunks, const float *mask, cudaStream_t st)
 {
-    sddmm_rows_kernel<G, R><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks);
+    sddmm_rows_kernel<G, R><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask);
 }
 
-}  // namespace
-
-extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
-                                   const int *column_indices, const float *lhs, const float *rhs,
-                                   float *out_values, void *stream)
+int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                 const int *column_indices, const float *mask, const float *lhs, const float *rhs,
+                 float *out_values, void *stream)
 {
     if (!ctx || M < 0 || K < 0 || N < 0 || nnz < 0) return DLSPM_ERR_INVALID_ARGUMENT;
     if (M > 0 && !row_offsets) return DLSPM_ERR_INVALID_ARGUMENT;
@@ -149,22 +148,38 @@ extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
     const int blocks = dlspm_ceil_div(M, kWarps);
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
-        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
-        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
-        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, st);
+        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
+        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
+        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, st);
     } else if (vec == 4) {
         // measured: 512-float segments (80 registers, 3 blocks per SM) win from N = 3136, 1024-float
         // segments below that
-        if (N > 2048) sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
-        else sddmm_rows_long_kernel<8><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4);
+        if (N > 2048) sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask);
+        else sddmm_rows_long_kernel<8><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask);
     } else if (vec == 2) {
-        sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+        sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask);
     } else {
-        sddmm_generic_kernel<1><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N);
+        sddmm_generic_kernel<1><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask);
     }
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                                   const int *column_indices, const float *lhs, const float *rhs,
+                                   float *out_values, void *stream)
+{
+    return sddmm_launch(ctx, M, K, N, nnz, row_offsets, column_indices, nullptr, lhs, rhs, out_values, stream);
+}
+
+extern "C" int dlspm_sddmm_csr_masked_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                                          const int *column_indices, const float *mask_values,
+                                          const float *lhs, const float *rhs, float *out_values, void *stream)
+{
+    return sddmm_launch(ctx, M, K, N, nnz, row_offsets, column_indices, mask_values, lhs, rhs, out_values, stream);
 }

@@ -49,8 +49,72 @@ __device__ __forceinline__ float mad(float a, float b, float c)
     else return fmaf(a, b, c);
 }
 
+// Adds the products of `cnt` staged (column, value) pairs to the accumulators of one warp slab, in
+// the order of the pairs.  J = 0: the plain loop, unrolled four times.  J > 0: J nonzeros are taken
+// at once, all their loads first and their products afterwards (still in pair order), which keeps
+// J*U loads in flight per lane; a lone small matrix is bound by exactly that latency chain.
+template <int VEC, int U, bool STRICT, int J>
+__device__ __forceinline__ void spmm_accumulate_staged(const int2 *stage, int cnt, const float *__restrict__ B,
+                                                       int N, const int (&cidx)[U], float (&acc)[U][VEC])
+{
+    if constexpr (J <= 1) {
+#pragma unroll 4
+        for (int j = 0; j < cnt; j++) {
+            const int2 e = stage[j];
+            const float a = __int_as_float(e.y);
+            const float *brow = B + (size_t)e.x * (size_t)N;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (cidx[u] < N) {
+                    float b[VEC];
+                    load_vec<VEC>(brow + cidx[u], b);
+#pragma unroll
+                    for (int v = 0; v < VEC; v++) acc[u][v] = mad<STRICT>(a, b[v], acc[u][v]);
+                }
+            }
+        }
+    } else {
+        for (int j = 0; j < cnt; j += J) {
+            float b[J][U][VEC];
+            float a[J];
+#pragma unroll
+            for (int jj = 0; jj < J; jj++) {
+                const bool live = j + jj < cnt;
+                const int2 e = stage[(j + jj) & 31];
+                a[jj] = __int_as_float(e.y);
+                const float *brow = B + (size_t)e.x * (size_t)N;
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if (live && cidx[u] < N) load_vec<VEC>(brow + cidx[u], b[jj][u]);
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < J; jj++) {
+                if (j + jj < cnt) {
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        if (cidx[u] < N) {
+#pragma unroll
+                            for (int v = 0; v < VEC; v++) acc[u][v] = mad<STRICT>(a[jj], b[jj][u][v], acc[u][v]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Nonzeros taken at once by a lone launch (0: the plain unrolled loop): 8 loads in flight per lane
+// for the one- and two-chunk slabs.  Measured on lone matrices of 256 to 2048 rows: 512 x 512 at
+// 10 %, N = 128 went from 7.7 to 5.2 us, 1024 x 1024 at 30 % from 20.5 to 17.5 us; 16 nonzeros at
+// once (one-chunk) or 8 (two-chunk) lost again through registers.  The grouped launch keeps the
+// plain loop for every width: it holds all three widths in one kernel, its occupancy is what
+// hides the latency there, and the batched loads would cost it registers.
+template <int U>
+constexpr int kLoneBatch = U == 1 ? 8 : U == 2 ? 4 : 0;
+
 // stage: 32 int2 slots private to this warp.
-template <int VEC, int U, bool STRICT>
+template <int VEC, int U, bool STRICT, int J = 0>
 __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
                                                    const int *__restrict__ cols, int start, int end,
                                                    const float *__restrict__ B, float *__restrict__ Crow,
@@ -71,22 +135,7 @@ __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ val
         if (p < end) cv = make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p)));
         stage[lane] = cv;
         __syncwarp();
-        const int cnt = min(32, end - base);
-#pragma unroll 4
-        for (int j = 0; j < cnt; j++) {
-            const int2 e = stage[j];
-            const float a = __int_as_float(e.y);
-            const float *brow = B + (size_t)e.x * (size_t)N;
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                if (cidx[u] < N) {
-                    float b[VEC];
-                    load_vec<VEC>(brow + cidx[u], b);
-#pragma unroll
-                    for (int v = 0; v < VEC; v++) acc[u][v] = mad<STRICT>(a, b[v], acc[u][v]);
-                }
-            }
-        }
+        spmm_accumulate_staged<VEC, U, STRICT, J>(stage, min(32, end - base), B, N, cidx, acc);
         __syncwarp();
     }
 #pragma unroll

@@ -111,6 +111,14 @@ int dlspm_sddmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int 
                         const int *column_indices, const float *lhs, const float *rhs,
                         float *out_values, void *stream);
 
+/* The same with the stored values of the mask as factors: out_values[p] = mask_values[p] * dot
+ * (the S_ij * (A_i . B_j) form).  mask_values may be NULL, which means 1.0 and is the reference's
+ * behaviour (its kernels never read the mask's values, SDDMM/sddmm-esimd-fromfile_v4.hpp:102-177).
+ * mask_values and out_values must not overlap. */
+int dlspm_sddmm_csr_masked_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                               const int *column_indices, const float *mask_values,
+                               const float *lhs, const float *rhs, float *out_values, void *stream);
+
 /* E[M x N] = (pattern(A) .* (C * B^T)) * D without writing the sampled products to memory.
  * C is M x N, B and D are K x N.  Replaces FusedEsimd(a_row_offsets, a_column_indices, c, b,
  * d, e, item) (FUSED/fused-esimd_cb.cpp:100-105); same result as Sddmm followed by Spmm

@@ -161,3 +161,32 @@ def test_full_size_outer_product_property(pkg, ctx, dev):
         w = (x * y).sum(dim=1)
         sc = (x.abs() * y.abs()).sum(dim=1)
         assert bool(((out[s:e].double() - w).abs() <= TOL * torch.maximum(w.abs(), sc)).all())
+
+
+@pytest.mark.parametrize("N", [3, 64, 128, 130, 2048])
+def test_mask_values_scale_the_products(pkg, oracle, ctx, dev, N):
+    """dlspm_sddmm_csr_masked_f32: S_ij * (A_i . B_j); a NULL mask is the reference's all-ones mask.
+    One kernel path per N here (scalar, two fast layouts, two-float vectors, segmented)."""
+    import torch
+
+    M, K = 90, 75
+    ro, ci = csr_bernoulli(pkg, M, K, 0.3, seed=900 + N)
+    nnz = int(ci.size)
+    lhs = dense(pkg, M, N, 900 + N, 11, kind=pkg.KIND_NORMAL)
+    rhs = dense(pkg, K, N, 900 + N, 12, kind=pkg.KIND_NORMAL)
+    mask = pkg.gen_dense_host(nnz, 900 + N, 2)
+    d = [to_dev(a, dev) for a in (ro, ci, mask, lhs, rhs)]
+    plain = torch.full((nnz,), float("nan"), device=dev)
+    masked = torch.full((nnz,), float("nan"), device=dev)
+    nomask = torch.full((nnz,), float("nan"), device=dev)
+    ctx.sddmm(M, K, N, nnz, d[0], d[1], d[3], d[4], plain)
+    ctx.sddmm_masked(M, K, N, nnz, d[0], d[1], d[2], d[3], d[4], masked)
+    ctx.sddmm_masked(M, K, N, nnz, d[0], d[1], None, d[3], d[4], nomask)
+    torch.cuda.synchronize()
+    plain, masked, nomask = plain.cpu().numpy(), masked.cpu().numpy(), nomask.cpu().numpy()
+    assert np.array_equal(plain.view(np.uint32), nomask.view(np.uint32))
+    assert np.array_equal(masked.view(np.uint32), (mask * plain).view(np.uint32))  # one rounding after the dot
+    ref = oracle.sddmm(ro, ci, lhs, rhs, M, N).astype(np.float64) * mask
+    scale = oracle.sddmm_scale(ro, ci, lhs, rhs, M, N) * np.abs(mask)
+    bad, worst = oracle.violations(ref.astype(np.float32), masked, scale.astype(np.float32), TOL)
+    assert bad == 0, worst
