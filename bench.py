@@ -263,6 +263,36 @@ def cpu_rate_probe(pkg, oracle, threads):
     return 2.0 * ci.size * N / t * 1e-9
 
 
+def cpu_variants(oracle, data, flops, dt_all, threads):
+    """The two other ways the reference's loop can be run on the host, on bounded sub-samples: one
+    thread, exactly as the reference's drivers call it, and a speed build (-O3 -march=native,
+    compiled on this machine) on all threads."""
+    out = {}
+    # one thread: a prefix of the sample worth about 3 s at 1/threads of the all-thread rate
+    budget = flops / dt_all / max(threads, 1) * 3.0
+    sub, f = [], 0.0
+    for d in data:
+        w = 2.0 * d[4].size * d[2]
+        if sub and f + w > budget:
+            break
+        sub.append(d)
+        f += w
+    t0 = time.perf_counter()
+    for (M, K, N, ro, ci, vals, B) in sub:
+        oracle.spmm(vals, ro, ci, B, M, N, threads=1)
+    out["single_thread"] = {"value": f / (time.perf_counter() - t0) * 1e-9, "unit": "GFLOP/s",
+                            "sample": f"{len(sub)} problems ({f / 1e9:.2f} GFLOP)"}
+    try:
+        speed = oracle.SpeedBuild()
+        t0 = time.perf_counter()
+        for (M, K, N, ro, ci, vals, B) in data:
+            speed.spmm(vals, ro, ci, B, M, N, max(threads, 2))
+        out["o3_march_native"] = {"value": flops / (time.perf_counter() - t0) * 1e-9, "unit": "GFLOP/s", "cores": threads}
+    except Exception as e:  # no compiler on the box: the figure is simply absent
+        out["o3_march_native"] = {"value": None, "why": str(e)[:120]}
+    return out
+
+
 def run_reference_arm(args, rank, world):
     """Times the reference's own CPU implementation of the path (the pinned oracle) on host cores."""
     if rank != 0:
@@ -792,7 +822,9 @@ def main():
             dt = time_cpu(oracle, data, threads)
             line["cpu_baseline"] = {"value": flops / dt * 1e-9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
                                     "sample": f"{len(data)} problems of the batch around the median cost "
-                                              f"({flops / 1e9:.2f} GFLOP, {dt:.1f} s)"}
+                                              f"({flops / 1e9:.2f} GFLOP, {dt:.1f} s)",
+                                    "build": "-O2 -ffp-contract=off (the build the parity tests pin)"}
+            line["cpu_baseline"].update(cpu_variants(oracle, data, flops, dt, threads))
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -64,6 +64,32 @@ def lib() -> C.CDLL:
     return _lib
 
 
+class SpeedBuild:
+    """The same oracle.c compiled for speed (-O3 -march=native) on the machine that runs it, for the
+    benchmark's CPU baseline only; the parity checks always use the -O2 -ffp-contract=off build."""
+
+    def __init__(self):
+        import shutil
+        import tempfile
+
+        cc = shutil.which("gcc")
+        if cc is None:
+            raise RuntimeError("no gcc on this machine")
+        self._dir = tempfile.mkdtemp(prefix="oracle_speed_")
+        path = os.path.join(self._dir, "liboracle_speed.so")
+        subprocess.run([cc, "-O3", "-march=native", "-fPIC", "-pthread", "-std=gnu11", "-shared", "-o", path,
+                        os.path.join(ORACLE_DIR, "oracle.c"), "-lm"], check=True, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT)
+        self._lib = C.CDLL(path)
+        self._lib.oracle_spmm_f32_mt.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I]
+
+    def spmm(self, values, row_offsets, cols, B, M, N, threads: int) -> np.ndarray:
+        values, row_offsets, cols, B = _f32(values), _i32(row_offsets), _i32(cols), _f32(B)
+        out = np.zeros((M, N), dtype=np.float32)
+        self._lib.oracle_spmm_f32_mt(_p(values), _p(row_offsets), _p(cols), _p(B), _p(out), M, N, threads)
+        return out
+
+
 def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
