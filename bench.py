@@ -290,7 +290,60 @@ def cpu_variants(oracle, data, flops, dt_all, threads):
         out["o3_march_native"] = {"value": flops / (time.perf_counter() - t0) * 1e-9, "unit": "GFLOP/s", "cores": threads}
     except Exception as e:  # no compiler on the box: the figure is simply absent
         out["o3_march_native"] = {"value": None, "why": str(e)[:120]}
+    # the same arithmetic with the loops interchanged (row of C innermost, unit stride): what a tuned
+    # CPU library does at least; bit-identical results, since every element still sums in CSR order
+    t0 = time.perf_counter()
+    for (M, K, N, ro, ci, vals, B) in data:
+        oracle.spmm(vals, ro, ci, B, M, N, threads=max(threads, 2), fast_order=True)
+    out["loops_interchanged"] = {"value": flops / (time.perf_counter() - t0) * 1e-9, "unit": "GFLOP/s", "cores": threads}
+    out["onemkl"] = time_onemkl(oracle, data, flops)
     return out
+
+
+def time_onemkl(oracle, data, flops):
+    """The reference's other CPU-side comparison is oneMKL's sparse BLAS (its MKL/ programs).  If
+    the single dynamic library is installed on this machine, mkl_sparse_s_mm is timed on the same
+    sample and checked against the oracle; otherwise the row says so."""
+    import ctypes as C
+
+    try:
+        mkl = C.CDLL("libmkl_rt.so")
+    except OSError:
+        return {"value": None, "why": "unavailable on this box (no libmkl_rt.so)"}
+    try:
+        class Descr(C.Structure):
+            _fields_ = [("type", C.c_int), ("mode", C.c_int), ("diag", C.c_int)]
+
+        create = mkl.mkl_sparse_s_create_csr
+        create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        mm = mkl.mkl_sparse_s_mm
+        mm.argtypes = [C.c_int, C.c_float, C.c_void_p, Descr, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_float,
+                       C.c_void_p, C.c_int]
+        destroy = mkl.mkl_sparse_destroy
+        destroy.argtypes = [C.c_void_p]
+        descr = Descr(20, 40, 50)  # general matrix
+        total, checked = 0.0, False
+        for (M, K, N, ro, ci, vals, B) in data:
+            ro32, ci32 = np.ascontiguousarray(ro, dtype=np.int32), np.ascontiguousarray(ci, dtype=np.int32)
+            v32, b32 = np.ascontiguousarray(vals, dtype=np.float32), np.ascontiguousarray(B, dtype=np.float32)
+            out = np.zeros((M, N), dtype=np.float32)
+            h = C.c_void_p()
+            if create(C.byref(h), 0, M, K, ro32.ctypes.data, ro32.ctypes.data + 4, ci32.ctypes.data, v32.ctypes.data):
+                return {"value": None, "why": "mkl_sparse_s_create_csr failed"}
+            t0 = time.perf_counter()
+            st = mm(10, 1.0, h, descr, 101, b32.ctypes.data, N, N, 0.0, out.ctypes.data, N)
+            total += time.perf_counter() - t0
+            destroy(h)
+            if st:
+                return {"value": None, "why": f"mkl_sparse_s_mm status {st}"}
+            if not checked:
+                ref = oracle.spmm(vals, ro, ci, B, M, N, threads=2)
+                if not np.allclose(out, ref, rtol=1e-4, atol=1e-4):
+                    return {"value": None, "why": "mkl_sparse_s_mm result differs from the oracle"}
+                checked = True
+        return {"value": flops / total * 1e-9, "unit": "GFLOP/s", "threads": "library default"}
+    except Exception as e:
+        return {"value": None, "why": f"oneMKL call failed: {str(e)[:100]}"}
 
 
 def run_reference_arm(args, rank, world):
