@@ -32,6 +32,7 @@ struct Options {
     bool cold = false;           // also time with L2 flushed between repetitions
     int device = 0;
     std::string csv;
+    bool graph = false;          // also time 100 launches captured in one CUDA graph (automatic below 10 us)
     bool cache = false;          // from-file drivers: keep a binary copy "<file>.csrbin" beside the text
     bool attention = false;      // fused driver: scale (and softmax) between the two products
     bool softmax = false;
@@ -53,6 +54,7 @@ inline Options parse(int argc, char **argv)
         else if (a == "--planned") o.planned = true;
         else if (a == "--cold") o.cold = true;
         else if (a == "--cache") o.cache = true;
+        else if (a == "--graph") o.graph = true;
         else if (a == "--softmax") o.attention = o.softmax = true;
         else if (a == "--scale") { o.attention = true; o.scale = (float)atof(next()); }
         else o.positional.push_back(a);
@@ -90,6 +92,60 @@ T *to_device(const std::vector<T> &h)
 // Minimum and median device time in ms of `reps` launches, each bracketed by events; the reference
 // reports the minimum (SPMM/spmm-esimd-fromfile.cpp:231-238).  With flush != nullptr a buffer
 // larger than L2 is rewritten before every launch.
+// Stream the timed launches go to: the default stream, except while a graph is being captured.
+inline void *&launch_stream()
+{
+    static void *s = nullptr;
+    return s;
+}
+
+// Per-launch time with `count` back-to-back launches captured in one CUDA graph, so that the gap
+// between a lone launch and its events (a few microseconds) does not count: the figure for
+// kernels that run less than about 10 us.
+template <class F>
+int time_graph(F &&launch, int count, double *ms_per_launch)
+{
+    cudaStream_t st;
+    DRV_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    launch_stream() = st;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = DLSPM_OK;
+    cudaError_t err = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    for (int i = 0; err == cudaSuccess && rc == DLSPM_OK && i < count; i++) rc = launch();
+    cudaError_t end_err = cudaStreamEndCapture(st, &graph);
+    launch_stream() = nullptr;
+    if (err == cudaSuccess) err = end_err;
+    if (err == cudaSuccess && rc == DLSPM_OK) err = cudaGraphInstantiate(&exec, graph, 0);
+    if (err != cudaSuccess || rc != DLSPM_OK) {
+        printf("graph timing skipped: %s\n", err != cudaSuccess ? cudaGetErrorString(err) : dlspm_strerror(rc));
+        if (graph) cudaGraphDestroy(graph);
+        cudaStreamDestroy(st);
+        cudaGetLastError();
+        return DLSPM_OK;
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    float best = 1e30f;
+    for (int r = 0; r < 6; r++) {  // the first replay warms up
+        cudaEventRecord(e0, st);
+        cudaGraphLaunch(exec, st);
+        cudaEventRecord(e1, st);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (r > 0 && ms < best) best = ms;
+    }
+    *ms_per_launch = (double)best / count;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    cudaStreamDestroy(st);
+    return DLSPM_OK;
+}
+
 template <typename F>
 int time_launches(F &&launch, int reps, float *flush, size_t flush_elems, double *min_ms, double *median_ms)
 {
@@ -220,8 +276,8 @@ inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, 
     if (o.planned) DRV_TRY(dlspm_plan_create(ctx, M, K, nnz, d_ro, d_ci, nullptr, &plan));
     printf("Start kernel execution\n");
     auto launch = [&]() {
-        return plan ? dlspm_spmm_csr_f32_planned(ctx, plan, N, d_v, d_ro, d_ci, d_B, d_C, nullptr)
-                    : dlspm_spmm_csr_f32(ctx, M, K, N, nnz, d_v, d_ro, d_ci, d_B, d_C, nullptr);
+        return plan ? dlspm_spmm_csr_f32_planned(ctx, plan, N, d_v, d_ro, d_ci, d_B, d_C, launch_stream())
+                    : dlspm_spmm_csr_f32(ctx, M, K, N, nnz, d_v, d_ro, d_ci, d_B, d_C, launch_stream());
     };
     double min_ms = 0, med_ms = 0;
     DRV_TRY(time_launches(launch, o.reps, nullptr, 0, &min_ms, &med_ms));
@@ -236,6 +292,11 @@ inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, 
     const double bytes = 4.0 * (M + 1) + 8.0 * nnz + 4.0 * (double)K * N + 4.0 * (double)M * N;
     printf("GFLOPS (2*nnz*N): %8.2f  algorithmic GB/s: %8.2f  median ms: %f\n", flops2 / (min_ms * 1e6),
            bytes / (min_ms * 1e6), med_ms);
+    if (o.graph || min_ms < 0.010) {
+        double g_ms = 0;
+        DRV_TRY(time_graph(launch, 100, &g_ms));
+        if (g_ms > 0) printf("graph of 100 launches: %f ms per launch  GFLOPS (2*nnz*N): %8.2f\n", g_ms, flops2 / (g_ms * 1e6));
+    }
     if (o.cold) {
         float *flush = nullptr;
         const size_t fe = (size_t)64 << 20;
@@ -288,7 +349,7 @@ inline int run_sddmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
         printf("device allocation failed\n");
         return DLSPM_ERR_NOMEM;
     }
-    auto launch = [&]() { return dlspm_sddmm_csr_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_l, d_r, d_o, nullptr); };
+    auto launch = [&]() { return dlspm_sddmm_csr_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_l, d_r, d_o, launch_stream()); };
     double min_ms = 0, med_ms = 0;
     DRV_TRY(time_launches(launch, o.reps, nullptr, 0, &min_ms, &med_ms));
     printf("MSZ = %d,  NSZ = %d  KSZ = %d\n", M, N, K);
@@ -299,6 +360,11 @@ inline int run_sddmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     const double bytes = 4.0 * (M + 1) + 8.0 * nnz + 4.0 * (double)M * N + 4.0 * (double)K * N;
     printf("GFLOPS (2*nnz*N): %8.2f  algorithmic GB/s: %8.2f  median ms: %f\n", 2.0 * nnz * N / (min_ms * 1e6),
            bytes / (min_ms * 1e6), med_ms);
+    if (o.graph || min_ms < 0.010) {
+        double g_ms = 0;
+        DRV_TRY(time_graph(launch, 100, &g_ms));
+        if (g_ms > 0) printf("graph of 100 launches: %f ms per launch  GFLOPS (2*nnz*N): %8.2f\n", g_ms, 2.0 * nnz * N / (g_ms * 1e6));
+    }
     if (o.cold) {
         float *flush = nullptr;
         const size_t fe = (size_t)64 << 20;
@@ -379,8 +445,8 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     auto launch = [&]() {
         if (o.attention)
             return dlspm_fused_attention_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, o.scale,
-                                             o.softmax ? DLSPM_ATTN_SOFTMAX : 0u, nullptr);
-        return dlspm_fused_sddmm_spmm_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, nullptr);
+                                             o.softmax ? DLSPM_ATTN_SOFTMAX : 0u, launch_stream());
+        return dlspm_fused_sddmm_spmm_f32(ctx, M, K, N, nnz, d_ro, d_ci, d_c, d_b, d_d, d_e, launch_stream());
     };
     double min_ms = 0, med_ms = 0;
     DRV_TRY(time_launches(launch, o.reps, nullptr, 0, &min_ms, &med_ms));
@@ -393,6 +459,11 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     const double bytes = 4.0 * (M + 1) + 4.0 * nnz + 4.0 * N * ((double)M + 2.0 * K) + 4.0 * (double)M * N;
     printf("GFLOPS (4*nnz*N): %8.2f  algorithmic GB/s: %8.2f  median ms: %f\n", 4.0 * nnz * N / (min_ms * 1e6),
            bytes / (min_ms * 1e6), med_ms);
+    if (o.graph || min_ms < 0.010) {
+        double g_ms = 0;
+        DRV_TRY(time_graph(launch, 100, &g_ms));
+        if (g_ms > 0) printf("graph of 100 launches: %f ms per launch  GFLOPS (4*nnz*N): %8.2f\n", g_ms, 4.0 * nnz * N / (g_ms * 1e6));
+    }
     DRV_CUDA(cudaMemcpy(e.data(), d_e, e.size() * sizeof(float), cudaMemcpyDeviceToHost));
     printf("checksum_e using gpu = %f\n", sqrt(mean_square(e.data(), e.size())));
     Diff d;

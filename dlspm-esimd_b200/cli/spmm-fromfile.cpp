@@ -1,7 +1,8 @@
 // SpMM from a pattern file: ./spmm-fromfile <filename>.smtx <batchsize> [options]
 // Same command line and report as the reference driver (SPMM/spmm-esimd-fromfile2.cpp:86-95).
 // Options: --reps n, --seed s, --csv file, --no-check, --signed, --planned, --cold, --device d,
-// --cache (binary copy of the parsed file beside it).  A file with a values block (fourth block of
+// --graph (also time 100 launches in one CUDA graph; automatic below 10 us), --cache (binary copy
+// of the parsed file beside it).  A file with a values block (fourth block of
 // nnz floats) is multiplied with those values instead of generated ones.
 #include "driver_common.hpp"
 

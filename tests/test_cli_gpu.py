@@ -41,6 +41,10 @@ def test_spmm_fromfile(pkg, tmp_path):
     # planned and signed variants give a report as well
     out = _run(pkg, "spmm-fromfile", smtx, 100, "--planned", "--signed", "--cold")
     assert "cold-L2 median ms" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+    # per-launch time from 100 launches captured in one CUDA graph (what counts for kernels of a few us)
+    out = _run(pkg, "spmm-fromfile", smtx, 64, "--graph")
+    assert 0 < _value(out, r"graph of 100 launches: ([0-9.e+-]+) ms per launch") < 1.0
+    assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
 
 
 def test_spmm_fromfile_cache_and_file_values(pkg, tmp_path):
@@ -86,8 +90,8 @@ def test_sddmm_fromfile_and_fused(pkg, tmp_path):
     assert "GFLOPS :" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-3
     row = open(csv).read().strip().split(",")
     assert len(row) == 7 and [int(row[0]), int(row[1]), int(row[2])] == [256, 128, 128]  # M,K,N,density,gflops,flops,max_diff
-    out = _run(pkg, "fused", 512, 512, 32, 0.1)
-    assert "GFLOPS/s :" in out and "checksum_e using gpu" in out
+    out = _run(pkg, "fused", 512, 512, 32, 0.1, "--graph")
+    assert "GFLOPS/s :" in out and "checksum_e using gpu" in out and "graph of 100 launches" in out
     assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
     out = _run(pkg, "fused", 256, 256, 64, 0.05, "--band", 8)
     assert _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-7
