@@ -38,33 +38,22 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
+// The passes base, base + stride, ... of one row: scores as in the SDDMM kernel, then the update of
+// the lane's partial output row.  On return acc holds this lane group's partial sums (relative to
+// run_max in softmax mode).
 template <int G, int R, int MODE>
-__global__ void __launch_bounds__(kWarps * 32)
-fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
-                  const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
-                  float *__restrict__ e, int M, int chunks, float scale)
+__device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, const float4 (&q)[R],
+                                                 const float4 *__restrict__ b4, const float4 *__restrict__ d4,
+                                                 int chunks, int start, int end, int stride, float scale, int lane,
+                                                 float4 (&acc)[R], float &run_max, float &run_sum)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarps + warp;
-    if (row >= M) return;
     const int g = lane / G, t = lane % G;
-    const float4 *c4 = reinterpret_cast<const float4 *>(c) + (size_t)row * (size_t)chunks;
-    const float4 *b4 = reinterpret_cast<const float4 *>(b);
-    const float4 *d4 = reinterpret_cast<const float4 *>(d);
-    float4 q[R];
-    load_row_chunks<G, R>(c4, chunks, t, q);
-    float4 acc[R];
-#pragma unroll
-    for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
     // column indices of the next pass are fetched one pass ahead
     int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
-    [[maybe_unused]] float run_max = -INFINITY, run_sum = 0.f;
-    for (int base = start; base < end; base += 32) {
+    for (int base = start; base < end; base += stride) {
         const int p = base + lane;
         const int col = col_next;
-        col_next = p + 32 < end ? __ldg(cols + p + 32) : -1;
+        col_next = p + stride < end ? __ldg(cols + p + stride) : -1;
         float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
         if constexpr (MODE == kScaled) score *= scale;
         if constexpr (MODE == kSoftmax) {
@@ -105,7 +94,7 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
             }
         }
     }
-    // add the partial rows of the 32/G groups
+    // add the partial rows of the 32/G groups: afterwards every lane holds the sums of its chunks
 #pragma unroll
     for (int s = G; s < 32; s <<= 1) {
 #pragma unroll
@@ -116,6 +105,28 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
             acc[r].w += __shfl_xor_sync(0xffffffffu, acc[r].w, s);
         }
     }
+}
+
+template <int G, int R, int MODE>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                  const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
+                  float *__restrict__ e, int M, int chunks, float scale)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const int g = lane / G, t = lane % G;
+    const float4 *c4 = reinterpret_cast<const float4 *>(c) + (size_t)row * (size_t)chunks;
+    float4 q[R];
+    load_row_chunks<G, R>(c4, chunks, t, q);
+    float4 acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float run_max = -INFINITY, run_sum = 0.f;
+    fused_row_passes<G, R, MODE>(cols, q, reinterpret_cast<const float4 *>(b), reinterpret_cast<const float4 *>(d),
+                                 chunks, __ldg(row_offsets + row), __ldg(row_offsets + row + 1), 32, scale, lane,
+                                 acc, run_max, run_sum);
     if constexpr (MODE == kSoftmax) {
         const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;  // empty row: zeros
 #pragma unroll
@@ -133,6 +144,104 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
             const int idx = r * G + t;
             if (idx < chunks) e4[idx] = acc[r];
         }
+    }
+}
+
+// Patterns with few rows: 1 << split_shift warps of a thread block share a row and take its passes
+// in turn; their partial rows (and, for the softmax, their running maxima and sums) are combined
+// through shared memory in a fixed order by the first warp of the row.
+template <int G, int R, int MODE>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_rows_split_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                        const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
+                        float *__restrict__ e, int M, int chunks, float scale, int split_shift)
+{
+    extern __shared__ float4 part[];  // [kWarps][G * R]
+    __shared__ float stat[kWarps][2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = blockIdx.x * kWarps + warp;
+    const int row = slot >> split_shift, sub = slot & ((1 << split_shift) - 1);
+    const bool active = row < M;
+    const int g = lane / G, t = lane % G;
+    float4 acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float run_max = -INFINITY, run_sum = 0.f;
+    if (active) {
+        const int start = __ldg(row_offsets + row) + 32 * sub, end = __ldg(row_offsets + row + 1);
+        if (start < end) {
+            const float4 *c4 = reinterpret_cast<const float4 *>(c) + (size_t)row * (size_t)chunks;
+            float4 q[R];
+            load_row_chunks<G, R>(c4, chunks, t, q);
+            fused_row_passes<G, R, MODE>(cols, q, reinterpret_cast<const float4 *>(b),
+                                         reinterpret_cast<const float4 *>(d), chunks, start, end, 32 << split_shift,
+                                         scale, lane, acc, run_max, run_sum);
+        }
+    }
+    if (sub != 0 && g == 0) {
+#pragma unroll
+        for (int r = 0; r < R; r++) part[warp * (G * R) + r * G + t] = acc[r];
+    }
+    if (lane == 0) {
+        stat[warp][0] = run_max;
+        stat[warp][1] = run_sum;
+    }
+    __syncthreads();
+    if (!active || sub != 0 || g != 0) return;
+    const int others = (1 << split_shift) - 1;
+    if constexpr (MODE == kSoftmax) {
+        float top = run_max;
+        for (int s = 1; s <= others; s++) top = fmaxf(top, stat[warp + s][0]);
+        if (top == -INFINITY) {  // empty row: zeros
+            run_sum = 0.f;
+        } else {
+            const float own = expf(run_max - top);
+            run_sum *= own;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                acc[r].x *= own;
+                acc[r].y *= own;
+                acc[r].z *= own;
+                acc[r].w *= own;
+            }
+            for (int s = 1; s <= others; s++) {
+                const float w = expf(stat[warp + s][0] - top);  // 0 for a warp that had no pass
+                run_sum += stat[warp + s][1] * w;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const float4 v = part[(warp + s) * (G * R) + r * G + t];
+                    acc[r].x = fmaf(w, v.x, acc[r].x);
+                    acc[r].y = fmaf(w, v.y, acc[r].y);
+                    acc[r].z = fmaf(w, v.z, acc[r].z);
+                    acc[r].w = fmaf(w, v.w, acc[r].w);
+                }
+            }
+        }
+        const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            acc[r].x *= inv;
+            acc[r].y *= inv;
+            acc[r].z *= inv;
+            acc[r].w *= inv;
+        }
+    } else {
+        for (int s = 1; s <= others; s++) {
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const float4 v = part[(warp + s) * (G * R) + r * G + t];
+                acc[r].x += v.x;
+                acc[r].y += v.y;
+                acc[r].z += v.z;
+                acc[r].w += v.w;
+            }
+        }
+    }
+    float4 *e4 = reinterpret_cast<float4 *>(e) + (size_t)row * (size_t)chunks;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int idx = r * G + t;
+        if (idx < chunks) e4[idx] = acc[r];
     }
 }
 
@@ -197,9 +306,31 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
 
 template <int G, int R, int MODE>
 void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
-                 int M, int chunks, float scale, cudaStream_t st)
+                 int M, int chunks, float scale, int split_shift, cudaStream_t st)
 {
+    if (split_shift > 0) {
+        const long long warps = (long long)M << split_shift;
+        const size_t smem = sizeof(float4) * (size_t)kWarps * G * R;
+        fused_rows_split_kernel<G, R, MODE><<<(unsigned)((warps + kWarps - 1) / kWarps), kWarps * 32, smem, st>>>(
+            ro, ci, c, b, d, e, M, chunks, scale, split_shift);
+        return;
+    }
     fused_rows_kernel<G, R, MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
+}
+
+// Warps per row (as a shift) for a pattern with few rows, by the rule of the SDDMM kernel: share
+// rows until about 32 warps per SM exist or a warp would get less than one full pass; leave
+// patterns alone that nearly fill one wave as they are.
+int fused_split_shift(const dlspm_ctx *ctx, int M, int N, int nnz)
+{
+    // two gathers per nonzero make a warp's pass heavier than in SDDMM: from N = 128 on, half as
+    // many warps already keep the L1 pipe busy (2048 x 512 at 20 %, N = 128 lost 17 % with more)
+    const long long want = (long long)ctx->sm_count * (N >= 128 ? 16 : 32);
+    if ((long long)M * 4 >= want * 3) return 0;
+    const double avg = (double)nnz / (double)(M > 0 ? M : 1);
+    int shift = 0;
+    while (shift < 3 && ((long long)M << shift) < want && avg > 32.0 * (1 << shift)) shift++;
+    return shift;
 }
 
 template <int MODE>
@@ -220,12 +351,13 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     int G = 0, R = 0;
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
-        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
-        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
-        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, st);
+        const int shift = fused_split_shift(ctx, M, N, nnz);
+        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
     } else {
         fused_generic_kernel<MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N, scale);
     }

@@ -118,3 +118,27 @@ def test_rejects_bad_arguments(pkg, ctx, dev):
         ctx.attention(4, 4, 4, 0, zi, zi, z, z, z, z, scale=float("nan"), flags=pkg.ATTN_SOFTMAX)
     with pytest.raises(pkg.DlspmError):
         ctx.attention(4, 4, 4, 0, zi, zi, z, z, z, z, scale=1.0, flags=8)
+
+
+@pytest.mark.parametrize("K,density,N", [(100, 0.5, 64), (300, 0.4, 32), (600, 0.5, 128), (600, 0.5, 1024)])
+@pytest.mark.parametrize("softmax", [False, True])
+def test_few_long_rows_are_shared_between_warps(pkg, oracle, ctx, dev, K, density, N, softmax):
+    """With few rows, 2, 4 or 8 warps share a row (about 50, 120 and 300 entries per row here) and
+    their partial rows, maxima and sums are combined; a few rows are emptied and a few shortened so
+    that some of the sharing warps have no pass at all."""
+    M = 40
+    ro, ci = csr_bernoulli(pkg, M, K, density, seed=41)
+    lengths = np.diff(ro).copy()
+    lengths[3] = 0
+    lengths[7] = 1
+    lengths[11] = 33
+    keep = np.concatenate([np.arange(ro[i], ro[i] + min(lengths[i], ro[i + 1] - ro[i])) for i in range(M)]).astype(np.int64)
+    ci = np.ascontiguousarray(ci[keep])
+    ro = np.concatenate([[0], np.cumsum(np.minimum(lengths, np.diff(ro)))]).astype(np.int32)
+    q = dense(pkg, M, N, 41, 11, kind=pkg.KIND_NORMAL)
+    k = dense(pkg, K, N, 41, 12, kind=pkg.KIND_NORMAL)
+    v = dense(pkg, K, N, 41, 13)
+    scale = 1.0 / np.sqrt(N)
+    out = run_attention(pkg, ctx, dev, M, K, N, ro, ci, q, k, v, scale, softmax)
+    check(oracle, ro, ci, q, k, v, M, N, scale, softmax, out)
+    assert (out[3] == 0).all()

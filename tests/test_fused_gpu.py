@@ -93,3 +93,15 @@ def test_matches_unfused_gpu_path(pkg, oracle, ctx, dev):
     scale = oracle.fused_scale(ro, ci, q, k, v, M, N)
     bad, worst = oracle.violations(e.cpu().numpy(), fused, scale, TOL)
     assert bad == 0, worst
+
+
+@pytest.mark.parametrize("K,density,N", [(100, 0.5, 64), (300, 0.4, 16), (600, 0.5, 128), (600, 0.5, 512)])
+def test_few_long_rows_are_shared_between_warps(pkg, oracle, ctx, dev, K, density, N):
+    """2, 4 or 8 warps per row (about 50, 120 and 300 entries per row) with their partial rows added
+    through shared memory."""
+    M = 40
+    ro, ci = csr_bernoulli(pkg, M, K, density, seed=43)
+    q = dense(pkg, M, N, 43, 11)
+    k = dense(pkg, K, N, 43, 12)
+    v = dense(pkg, K, N, 43, 13)
+    check(oracle, ro, ci, q, k, v, M, N, run_fused(ctx, dev, M, K, N, ro, ci, q, k, v))
