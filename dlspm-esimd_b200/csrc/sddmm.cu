@@ -16,16 +16,18 @@ namespace {
 constexpr int kWarps = 8;
 
 // `mask` (may be null) holds one factor per stored entry: out[p] = mask[p] * dot.
-template <int G, int R>
+template <int G, int R, bool KSPLIT>
 __global__ void __launch_bounds__(kWarps * 32)
 sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
-                  int M, int chunks, const float *__restrict__ mask, int split_shift)
+                  int M, int chunks, const float *__restrict__ mask, int split_shift, int k_shift)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // 1 << split_shift warps share a row and take its passes of 32 nonzeros in turn (the outputs
-    // of different nonzeros are independent, so nothing is combined afterwards)
-    const int slot = blockIdx.x * kWarps + warp;
+    // (1 << split_shift) * (1 << k_shift) warps share a row: the passes of 32 nonzeros are dealt
+    // out in turn, and within a pass a warp takes every (1 << k_shift)-th nonzero of each lane
+    // group.  The outputs of different nonzeros are independent, so nothing is combined afterwards.
+    const int slot = (blockIdx.x * kWarps + warp) >> k_shift;
+    const int kmask = (1 << k_shift) - 1, ksub = (blockIdx.x * kWarps + warp) & kmask;
     const int row = slot >> split_shift;
     if (row >= M) return;
     const int stride = 32 << split_shift;
@@ -44,23 +46,26 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
         const int p = base + lane;
         const int col = col_next;
         col_next = p + stride < end ? __ldg(cols + p + stride) : -1;
-        const float r = sddmm_pass<G, R>(a, rhs4, chunks, col, g, t);
-        if (p < end) out[p] = mask ? __ldg(mask + p) * r : r;
+        const float r = sddmm_pass<G, R, KSPLIT>(a, rhs4, chunks, col, g, t, kmask, ksub);
+        if (p < end && (!KSPLIT || (t & kmask) == ksub)) out[p] = mask ? __ldg(mask + p) * r : r;
     }
 }
 
 // Inner dimension beyond 1024 (16-byte aligned rows): the lanes' partial dot products of a pass are
 // accumulated over segments of 32*R float4 and reduced once at the end of the pass; the lhs segment
 // is re-read from L1 for every pass, which adds 3 % to the rhs traffic.
-template <int R>
+template <int R, bool KSPLIT>
 __global__ void __launch_bounds__(kWarps * 32)
 sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                        const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
-                       int M, int chunks, const float *__restrict__ mask)
+                       int M, int chunks, const float *__restrict__ mask, int k_shift)
 {
     constexpr int G = 32, kSeg = G * R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarps + warp;
+    // 1 << k_shift warps share a row, each taking every (1 << k_shift)-th nonzero of a pass
+    const int slot = blockIdx.x * kWarps + warp;
+    const int kmask = (1 << k_shift) - 1, ksub = slot & kmask;
+    const int row = slot >> k_shift;
     if (row >= M) return;
     const float4 *lhs4 = reinterpret_cast<const float4 *>(lhs) + (size_t)row * (size_t)chunks;
     const float4 *rhs4 = reinterpret_cast<const float4 *>(rhs);
@@ -77,10 +82,10 @@ sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restric
             const int len = min(kSeg, chunks - seg);
             float4 a[R];
             load_row_chunks<G, R>(lhs4 + seg, len, lane, a);
-            sddmm_accumulate<G, R>(part, a, rhs4 + seg, len, chunks, col, 0, lane);
+            sddmm_accumulate<G, R, KSPLIT>(part, a, rhs4 + seg, len, chunks, col, 0, lane, kmask, ksub);
         }
         group_transpose_reduce<G>(part, lane);
-        if (p < end) out[p] = mask ? __ldg(mask + p) * part[0] : part[0];
+        if (p < end && (!KSPLIT || (lane & kmask) == ksub)) out[p] = mask ? __ldg(mask + p) * part[0] : part[0];
     }
 }
 
@@ -128,11 +133,14 @@ sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
 
 template <int G, int R>
 void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M,
-                 int chunks, const float *mask, int split_shift, cudaStream_t st)
+                 int chunks, const float *mask, int split_shift, int k_shift, cudaStream_t st)
 {
-    const long long warps = (long long)M << split_shift;
-    sddmm_rows_kernel<G, R><<<(unsigned)((warps + kWarps - 1) / kWarps), kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask,
-                                                                                  split_shift);
+    const long long warps = (long long)M << (split_shift + k_shift);
+    const unsigned blocks = (unsigned)((warps + kWarps - 1) / kWarps);
+    if (k_shift > 0)
+        sddmm_rows_kernel<G, R, true><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask, split_shift, k_shift);
+    else
+        sddmm_rows_kernel<G, R, false><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask, split_shift, 0);
 }
 
 // Warps per row (as a shift) for a pattern with few rows: one warp per row would leave most of the
@@ -149,6 +157,25 @@ int sddmm_split_shift(const dlspm_ctx *ctx, int M, int nnz)
     int shift = 0;
     while (shift < 3 && ((long long)M << shift) < want && avg > 32.0 * (1 << shift)) shift++;
     return shift;
+}
+
+// Further sharing inside a pass for patterns that are still far from filling the device (few and
+// short rows, e.g. a 64 x 576 layer with a long inner dimension): each of 2, 4 or 8 warps takes
+// every 2nd, 4th or 8th nonzero of a lane group.  `shared` = warps per row already decided.
+// `min_row`: shortest average row for which this is done.  Every sharing warp loads the lhs row and
+// runs the butterfly again, and the kernel with the extra test batches fewer loads; measured on the
+// register-resident path, 512 x 128 at 10 % (13 nonzeros per row, N = 784) lost 16 to 35 % at any
+// sharing factor while 128 x 512 (51 per row) gained 2.2x, so short rows are left alone there.
+// With a long inner dimension (segmented kernel) every case measured gained (64 x 576, N = 3136:
+// 112 -> 43 us; 64 x 64: 23 -> 15 us).
+int sddmm_k_shift(const dlspm_ctx *ctx, int M, int nnz, int shared_shift, double min_row)
+{
+    const long long want = (long long)ctx->sm_count * 32;
+    const double avg = (double)nnz / (double)(M > 0 ? M : 1);
+    if (avg < min_row) return 0;
+    int k = 0;
+    while (k < 3 && ((long long)M << (shared_shift + k)) * 2 <= want) k++;
+    return k;
 }
 
 int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
@@ -173,17 +200,22 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
         const int shift = sddmm_split_shift(ctx, M, nnz);
-        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
-        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
-        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, st);
+        const int kshift = sddmm_k_shift(ctx, M, nnz, shift, 16.0);
+        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
+        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
+        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, st);
     } else if (vec == 4) {
         // measured: 512-float segments (80 registers, 3 blocks per SM) win from N = 3136, 1024-float
         // segments below that
-        if (N > 2048) sddmm_rows_long_kernel<4><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask);
-        else sddmm_rows_long_kernel<8><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask);
+        const int kshift = sddmm_k_shift(ctx, M, nnz, 0, 0.0);
+        const unsigned lblocks = (unsigned)((((long long)M << kshift) + kWarps - 1) / kWarps);
+        if (N > 2048 && kshift > 0) sddmm_rows_long_kernel<4, true><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, kshift);
+        else if (N > 2048) sddmm_rows_long_kernel<4, false><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, 0);
+        else if (kshift > 0) sddmm_rows_long_kernel<8, true><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, kshift);
+        else sddmm_rows_long_kernel<8, false><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, 0);
     } else if (vec == 2) {
         sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask);
     } else {

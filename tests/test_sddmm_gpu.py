@@ -190,3 +190,14 @@ def test_mask_values_scale_the_products(pkg, oracle, ctx, dev, N):
     scale = oracle.sddmm_scale(ro, ci, lhs, rhs, M, N) * np.abs(mask)
     bad, worst = oracle.violations(ref.astype(np.float32), masked, scale.astype(np.float32), TOL)
     assert bad == 0, worst
+
+
+@pytest.mark.parametrize("M,K,N,density", [(64, 576, 3136, 0.1), (64, 64, 3136, 0.1), (128, 512, 784, 0.1),
+                                           (512, 128, 784, 0.1), (256, 256, 64, 0.5), (2, 300, 128, 0.9)])
+def test_tiny_patterns_share_rows_and_passes(pkg, oracle, ctx, dev, M, K, N, density):
+    """Layer-sized patterns (tens to hundreds of rows): warps share a row's passes and, where the
+    device would still be mostly idle, the nonzeros inside a pass."""
+    ro, ci = csr_bernoulli(pkg, M, K, density, seed=1000 + M + N)
+    lhs = dense(pkg, M, N, 1000 + M, 11, kind=pkg.KIND_NORMAL)
+    rhs = dense(pkg, K, N, 1000 + M, 12, kind=pkg.KIND_NORMAL)
+    check(oracle, ro, ci, lhs, rhs, M, N, run_sddmm(ctx, dev, M, K, N, ro, ci, lhs, rhs))
