@@ -15,6 +15,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <chrono>
 #include <string>
 #include <vector>
 
@@ -273,7 +274,14 @@ inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, 
     }
     printf("copy to device completed\n");
     dlspm_plan *plan = nullptr;
-    if (o.planned) DRV_TRY(dlspm_plan_create(ctx, M, K, nnz, d_ro, d_ci, nullptr, &plan));
+    if (o.planned) {
+        // set-up time is reported on its own line, never inside the kernel time
+        cudaDeviceSynchronize();
+        const auto t0 = std::chrono::steady_clock::now();
+        DRV_TRY(dlspm_plan_create(ctx, M, K, nnz, d_ro, d_ci, nullptr, &plan));
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        printf("plan (rows binned by length) created in %f ms\n", ms);
+    }
     printf("Start kernel execution\n");
     auto launch = [&]() {
         return plan ? dlspm_spmm_csr_f32_planned(ctx, plan, N, d_v, d_ro, d_ci, d_B, d_C, launch_stream())

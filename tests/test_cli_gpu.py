@@ -41,6 +41,7 @@ def test_spmm_fromfile(pkg, tmp_path):
     # planned and signed variants give a report as well
     out = _run(pkg, "spmm-fromfile", smtx, 100, "--planned", "--signed", "--cold")
     assert "cold-L2 median ms" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+    assert _value(out, r"plan \(rows binned by length\) created in ([0-9.e+-]+) ms") > 0
     # per-launch time from 100 launches captured in one CUDA graph (what counts for kernels of a few us)
     out = _run(pkg, "spmm-fromfile", smtx, 64, "--graph")
     assert 0 < _value(out, r"graph of 100 launches: ([0-9.e+-]+) ms per launch") < 1.0
