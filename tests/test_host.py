@@ -164,7 +164,9 @@ def test_csr_cache_empty_matrix(pkg, tmp_path):
 
 def test_reader_matches_fscanf_reader_on_dataset_files(pkg, oracle):
     """Bit-exact index handling on real pattern files, where the dataset checkout is present."""
-    root = os.path.join(os.environ.get("DLSPM_REFERENCE_DIR", "/root/reference"), "dlmc")
+    import __graft_entry__ as entry
+
+    root = os.path.join(entry.REFERENCE_DIR, "dlmc")
     files = sorted(glob.glob(os.path.join(root, "rn50", "*", "*", "*.smtx")))
     files += sorted(glob.glob(os.path.join(root, "transformer", "*", "*", "*.smtx")))
     if not files:
