@@ -254,3 +254,41 @@ def test_full_size_row_sum_property(pkg, ctx, dev):
     want = isum[ro[1:].long()] - isum[ro[:-1].long()]
     assert bool(((Cd[:, 0].double() - want).abs() <= TOL * want.clamp(min=1.0)).all())
     assert bool((Cd == Cd[:, :1]).all())
+
+
+@pytest.mark.parametrize("K,density", [(40, 0.5), (100, 0.5), (600, 0.5)])
+@pytest.mark.parametrize("N", [32, 50, 128, 256, 1024, 3136])
+@pytest.mark.parametrize("plan", [False, True])
+def test_few_rows_are_shared_between_warps(pkg, oracle, ctx, dev, K, density, N, plan):
+    """A lone matrix with few rows runs with 2, 4 or 8 warps per row (about 20, 50 and 300 entries per
+    row here), partial slabs combined through shared memory; empty and one-entry rows included, all
+    slab widths and the scalar path (N = 50)."""
+    M = 40
+    ro, ci = csr_bernoulli(pkg, M, K, density, seed=51 + K)
+    lengths = np.diff(ro).copy()
+    lengths[2], lengths[9] = 0, 1
+    keep = np.concatenate([np.arange(ro[i], ro[i] + min(lengths[i], ro[i + 1] - ro[i])) for i in range(M)]).astype(np.int64)
+    ci = np.ascontiguousarray(ci[keep])
+    ro = np.concatenate([[0], np.cumsum(np.minimum(lengths, np.diff(ro)))]).astype(np.int32)
+    vals = pkg.gen_dense_host(int(ci.size), 51, 2)
+    B = dense(pkg, K, N, 51, 10)
+    out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B, plan=plan)
+    check(oracle, ro, ci, vals, B, M, N, out)
+    assert (out[2] == 0).all()
+
+
+def test_strict_mode_keeps_csr_order_with_batched_loads(pkg, oracle, ctx, dev):
+    """Strict mode never shares rows, and the narrow slabs' batched loads keep the order of the
+    products: bits of the host loop for one-, two- and four-chunk slabs and ragged row lengths."""
+    M, K = 70, 300
+    ro, ci = csr_from_lengths(pkg, K, [0, 1, 3, 4, 5, 7, 8, 9, 15, 16, 17, 31, 32, 33, 40, 63, 64, 65, 200, 300] + [11] * 50, seed=61)
+    vals = pkg.gen_dense_host(int(ci.size), 61, 2)
+    ctx.set_option(pkg.OPT_STRICT_FP32, 1)
+    try:
+        for N in (128, 100, 256, 1024):
+            B = dense(pkg, K, N, 61, 10)
+            out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+            ref = oracle.spmm(vals, ro, ci, B, M, N)
+            assert np.array_equal(out.view(np.uint32), ref.view(np.uint32)), N
+    finally:
+        ctx.set_option(pkg.OPT_STRICT_FP32, 0)
