@@ -25,9 +25,10 @@ struct SpmmArgs {
     int M, N;
     int row_groups;  // ceil(M / 8)
     int chunks;      // column chunks per slab (<= compiled U)
+    int sm_count;
 };
 
-template <int VEC, int U, bool STRICT>
+template <int VEC, int U, bool STRICT, int J>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const SpmmArgs a)
 {
     __shared__ int2 stage[kWarpsPerCta][32];
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_kernel(const Spmm
     if (slot >= a.M) return;
     const int row = a.row_order ? a.row_order[slot] : slot;
     const int start = __ldg(a.row_offsets + row), end = __ldg(a.row_offsets + row + 1);
-    spmm_warp_row_slab<VEC, U, STRICT, kLoneBatch<U>>(a.values, a.cols, start, end, a.B,
+    spmm_warp_row_slab<VEC, U, STRICT, J>(a.values, a.cols, start, end, a.B,
                                        a.C + (size_t)row * (size_t)a.N, a.N, slab * 32 * VEC * U, lane,
                                        stage[warp]);
 }
@@ -171,8 +172,20 @@ void launch_rows(const SpmmArgs &a, int slabs, bool strict, cudaStream_t st)
 {
     const long long tiles = (long long)a.row_groups * slabs;
     dim3 grid((unsigned)tiles), block(kWarpsPerCta * 32);
-    if (strict) spmm_rows_kernel<VEC, U, true><<<grid, block, 0, st>>>(a);
-    else spmm_rows_kernel<VEC, U, false><<<grid, block, 0, st>>>(a);
+    // The narrow slabs exist in two builds: with the batched loads (74 to 76 registers, three
+    // resident blocks) for launches of a few waves, where the latency chain of a warp counts, and
+    // with the plain loop (32 and 44 registers) for long launches, where occupancy hides it.
+    // Measured: one-chunk slabs, 32768 x 8192 (9 waves) 0.71 -> 0.61 ms with the plain loop but
+    // 8192 x 8192 (2.3 waves) 0.19 -> 0.20 ms; two-chunk slabs, 32768 x 2048 413 -> 338 us.
+    const int waves = U == 1 ? 6 : 2;
+    const bool lone = kLoneBatch<U> > 0 && tiles <= (long long)waves * 3 * a.sm_count;
+    if (lone) {
+        if (strict) spmm_rows_kernel<VEC, U, true, kLoneBatch<U>><<<grid, block, 0, st>>>(a);
+        else spmm_rows_kernel<VEC, U, false, kLoneBatch<U>><<<grid, block, 0, st>>>(a);
+    } else {
+        if (strict) spmm_rows_kernel<VEC, U, true, 0><<<grid, block, 0, st>>>(a);
+        else spmm_rows_kernel<VEC, U, false, 0><<<grid, block, 0, st>>>(a);
+    }
 }
 
 template <int VEC, int U>
@@ -219,7 +232,7 @@ int spmm_launch(dlspm_ctx *ctx, int M, int N, int nnz, const float *values, cons
                 const int *cols, const float *B, float *C, const int *row_order, cudaStream_t st)
 {
     if (M == 0 || N == 0) return DLSPM_OK;
-    SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1};
+    SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1, ctx->sm_count};
     const int vec = dlspm_vec_width(N, B, C);
     const bool strict = ctx->strict_fp32 != 0;
     const int split = spmm_row_split(ctx, M, N, nnz, vec, strict);
@@ -360,7 +373,7 @@ extern "C" int dlspm_spmm_csr_f32_scatter(dlspm_ctx *ctx, int M, int K, int N, i
     if (rc) return rc;
     if (M == 0 || N == 0) return DLSPM_OK;
     ScatterArgs s;
-    s.a = SpmmArgs{values, row_offsets, column_indices, B, nullptr, nullptr, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1};
+    s.a = SpmmArgs{values, row_offsets, column_indices, B, nullptr, nullptr, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1, ctx->sm_count};
     s.first_row = first_row;
     s.ndst = ndst;
     const void *align_probe = B;
