@@ -19,9 +19,11 @@ constexpr int kWarps = 8;
 // CAP: compiled for eight resident thread blocks (32 registers).  For the two-chunk layout (inner
 // dimension 36 to 64) that is 1.5 to 1.65x faster once the pattern has more rows than fit the device
 // at once (8192 x 8192, N = 64: 156 -> 94 us) and 13 % slower below that (4096 rows), so the launcher
-// picks by the number of warps.  The one-chunk layout needs 32 registers anyway.
+// picks by the number of warps.  The one-chunk layout needs 32 registers anyway.  The 32-lane layouts
+// are held to five (four chunks per lane) and four (eight chunks) resident blocks: 8192 x 2048 with
+// N = 512 went 296 -> 255 us, with N = 1024 754 -> 480 us; one block more lost 15 to 35 % again.
 template <int G, int R, bool KSPLIT, bool CAP = false>
-__global__ void __launch_bounds__(kWarps * 32, CAP ? 8 : 0)
+__global__ void __launch_bounds__(kWarps * 32, CAP ? 8 : ((G == 32 && R == 4 && !KSPLIT) ? 5 : ((G == 32 && R == 8 && !KSPLIT) ? 4 : 0)))
 sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
                   int M, int chunks, const float *__restrict__ mask, int split_shift, int k_shift)
@@ -58,8 +60,9 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
 // Inner dimension beyond 1024 (16-byte aligned rows): the lanes' partial dot products of a pass are
 // accumulated over segments of 32*R float4 and reduced once at the end of the pass; the lhs segment
 // is re-read from L1 for every pass, which adds 3 % to the rhs traffic.
+// (512-float segments: held to four resident blocks, 8192 x 2048 with N = 3136 1766 -> 1629 us.)
 template <int R, bool KSPLIT>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, (R == 4 && !KSPLIT) ? 4 : 0)
 sddmm_rows_long_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                        const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
                        int M, int chunks, const float *__restrict__ mask, int k_shift)
