@@ -110,8 +110,11 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
 // Feature dimensions up to 32 (one float4 per lane): capped at 32 registers for eight resident
 // thread blocks, which measured 1.2 to 1.6x faster there (8192 x 2048, d = 32: 55 -> 33 us); the
 // same cap on the two-chunk layout (d = 64) lost 10 to 20 %.
-template <int G, int R, int MODE>
-__global__ void __launch_bounds__(kWarps * 32, (G == 8 && R == 1) ? 8 : 0)
+// CAP: a second build of the 32-lane, four-chunk layout (d = 260..512) held to four resident blocks
+// (64 registers instead of 126): 1.3 to 1.5x faster once the pattern has more rows than the
+// uncapped build keeps resident (8192 x 2048, d = 512: 637 -> 479 us), 12 % slower below that.
+template <int G, int R, int MODE, bool CAP = false>
+__global__ void __launch_bounds__(kWarps * 32, (G == 8 && R == 1) ? 8 : (CAP ? 4 : 0))
 fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
                   float *__restrict__ e, int M, int chunks, float scale)
@@ -309,7 +312,7 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
 
 template <int G, int R, int MODE>
 void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
-                 int M, int chunks, float scale, int split_shift, cudaStream_t st)
+                 int M, int chunks, float scale, int split_shift, int sm_count, cudaStream_t st)
 {
     if (split_shift > 0) {
         const long long warps = (long long)M << split_shift;
@@ -317,6 +320,12 @@ void launch_fast(const int *ro, const int *ci, const float *c, const float *b, c
         fused_rows_split_kernel<G, R, MODE><<<(unsigned)((warps + kWarps - 1) / kWarps), kWarps * 32, smem, st>>>(
             ro, ci, c, b, d, e, M, chunks, scale, split_shift);
         return;
+    }
+    if constexpr (G == 32 && R == 4) {
+        if ((long long)M > 2LL * kWarps * sm_count) {  // more rows than two resident blocks per SM hold
+            fused_rows_kernel<G, R, MODE, true><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
+            return;
+        }
     }
     fused_rows_kernel<G, R, MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
 }
@@ -355,12 +364,12 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
         const int shift = fused_split_shift(ctx, M, N, nnz);
-        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
-        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
-        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, st);
+        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
     } else {
         fused_generic_kernel<MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N, scale);
     }
