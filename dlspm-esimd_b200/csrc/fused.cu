@@ -107,14 +107,16 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
     }
 }
 
-// Feature dimensions up to 32 (one float4 per lane): capped at 32 registers for eight resident
-// thread blocks, which measured 1.2 to 1.6x faster there (8192 x 2048, d = 32: 55 -> 33 us); the
-// same cap on the two-chunk layout (d = 64) lost 10 to 20 %.
-// CAP: a second build of the 32-lane, four-chunk layout (d = 260..512) held to four resident blocks
-// (64 registers instead of 126): 1.3 to 1.5x faster once the pattern has more rows than the
-// uncapped build keeps resident (8192 x 2048, d = 512: 637 -> 479 us), 12 % slower below that.
+// CAP: second builds with a register cap, chosen per launch.
+//  - one chunk per lane (d <= 32): 32 registers for eight resident blocks instead of six.  It pays
+//    when it saves a wave of thread blocks: 8192 rows are 1.15 waves of six blocks per SM but fit
+//    one wave of eight (55 -> 33 us at 8192 x 2048, d = 32); with both in one wave (4096 rows) or
+//    many waves (32768 rows) the 40-register build is 7 to 8 % faster.
+//  - 32 lanes x four chunks (d = 260..512): 64 registers for four resident blocks instead of two:
+//    1.3 to 1.5x faster once the pattern has more rows than the uncapped build keeps resident
+//    (8192 x 2048, d = 512: 637 -> 479 us), 12 % slower below that.
 template <int G, int R, int MODE, bool CAP = false>
-__global__ void __launch_bounds__(kWarps * 32, (G == 8 && R == 1) ? 8 : (CAP ? 4 : 0))
+__global__ void __launch_bounds__(kWarps * 32, CAP ? (G == 8 ? 8 : 4) : 0)
 fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
                   float *__restrict__ e, int M, int chunks, float scale)
@@ -324,6 +326,15 @@ void launch_fast(const int *ro, const int *ci, const float *c, const float *b, c
     if constexpr (G == 32 && R == 4) {
         if ((long long)M > 2LL * kWarps * sm_count) {  // more rows than two resident blocks per SM hold
             fused_rows_kernel<G, R, MODE, true><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
+            return;
+        }
+    }
+    if constexpr (G == 8 && R == 1) {
+        // waves of thread blocks times blocks per wave, the capped build 7 % slower per block
+        const long long blocks = dlspm_ceil_div(M, kWarps);
+        const long long w6 = (blocks + 6LL * sm_count - 1) / (6LL * sm_count), w8 = (blocks + 8LL * sm_count - 1) / (8LL * sm_count);
+        if ((double)w8 * 8.0 * 1.07 < (double)w6 * 6.0) {
+            fused_rows_kernel<G, R, MODE, true><<<(unsigned)blocks, kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
             return;
         }
     }

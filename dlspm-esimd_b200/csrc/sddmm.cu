@@ -145,7 +145,9 @@ void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rh
     const long long warps = (long long)M << (split_shift + k_shift);
     const unsigned blocks = (unsigned)((warps + kWarps - 1) / kWarps);
     if constexpr (G == 8 && R == 2) {
-        if (k_shift == 0 && warps > 6LL * kWarps * sm_count) {  // more than the uncapped build keeps resident
+        // the capped build pays when it saves a wave of thread blocks (eight instead of six per SM)
+        const long long w6 = (blocks + 6LL * sm_count - 1) / (6LL * sm_count), w8 = (blocks + 8LL * sm_count - 1) / (8LL * sm_count);
+        if (k_shift == 0 && (double)w8 * 8.0 * 1.07 < (double)w6 * 6.0) {
             sddmm_rows_kernel<G, R, false, true><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask, split_shift, 0);
             return;
         }
