@@ -692,6 +692,29 @@ def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
 
 # ---- main arm ------------------------------------------------------------------------------------------------------
 
+def bind_to_gpu_cpus(local_rank):
+    """With several ranks on one host the pinned staging buffers of a rank should live on the NUMA
+    node of its GPU (first touch places them where the rank runs), or eight ranks pull their copies
+    through one socket.  This restricts the rank's own CPU affinity to the CPUs NVML names for the
+    GPU, when the process is allowed to run on any of them; nothing about the GPU is changed."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        ideal = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        both = ideal & allowed
+        note = f"[rank {local_rank}] cpus allowed {len(allowed)}, near the GPU {len(ideal)}, both {len(both)}"
+        if both and both != allowed:
+            os.sched_setaffinity(0, both)
+            note += " -> bound"
+        print(note, file=sys.stderr, flush=True)
+    except Exception as e:  # no NVML, or the query is not supported: run unbound
+        print(f"[rank {local_rank}] cpu binding skipped: {str(e)[:80]}", file=sys.stderr, flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -723,6 +746,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        bind_to_gpu_cpus(local_rank)
         dist.init_process_group("nccl", device_id=dev)
 
     pkg = entry.load_package()
