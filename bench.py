@@ -484,6 +484,29 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
     out["fused_band4096_d64"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 4.0 * nnz * N,
                                           4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N, hbm_gbs, fp32_tflops)
 
+    # the same two kernels on patterns large enough to fill the device (the shapes of the ncu summaries)
+    M, K, N = 8192, 2048, 128
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.2, 22)
+    nnz = int(ci.size)
+    s2 = [up(ro), up(ci), up(pkg.gen_dense_host(M * N, 22, 11, kind=2)), up(pkg.gen_dense_host(K * N, 22, 12, kind=2)),
+          torch.empty(nnz, device=dev)]
+    fn = lambda: ctx.sddmm(M, K, N, nnz, *s2)
+    fn(); fn()
+    out["sddmm_8192x2048_d0.2_n128"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 2.0 * nnz * N,
+                                                  4 * (M + 1) + 8 * nnz + 4 * M * N + 4 * K * N, hbm_gbs, fp32_tflops)
+    M, K, N = 16384, 4096, 64
+    ro, ci = pkg.gen_bernoulli_csr_host(M, K, 0.066, 23)
+    nnz = int(ci.size)
+    f2 = [up(ro), up(ci), up(pkg.gen_dense_host(M * N, 23, 11, kind=2)), up(pkg.gen_dense_host(K * N, 23, 12, kind=2)),
+          up(pkg.gen_dense_host(K * N, 23, 13, kind=2)), torch.empty(M * N, device=dev)]
+    fn = lambda: ctx.fused(M, K, N, nnz, *f2)
+    fn(); fn()
+    out["fused_16384x4096_d0.066_n64"] = summarize(time_graph(fn), time_kernel(fn, reps, flush), 4.0 * nnz * N,
+                                                   4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N, hbm_gbs, fp32_tflops)
+    M = K = 4096
+    N = 64
+    nnz = int(f[1].numel())
+
     # the same chain as sparse attention: scale 1/sqrt(d) and a row softmax between the two products
     fn = lambda: ctx.attention(M, K, N, nnz, *f, scale=N ** -0.5, flags=pkg.ATTN_SOFTMAX)
     fn(); fn()
