@@ -228,14 +228,25 @@ int spmm_row_split(const dlspm_ctx *ctx, int M, int N, int nnz, int vec, bool st
 }
 
 
+// max_row_len: longest row if known (from a plan), else 0.
 int spmm_launch(dlspm_ctx *ctx, int M, int N, int nnz, const float *values, const int *row_offsets,
-                const int *cols, const float *B, float *C, const int *row_order, cudaStream_t st)
+                const int *cols, const float *B, float *C, const int *row_order, int max_row_len, cudaStream_t st)
 {
     if (M == 0 || N == 0) return DLSPM_OK;
     SpmmArgs a{values, row_offsets, cols, B, C, row_order, M, N, dlspm_ceil_div(M, kWarpsPerCta), 1, ctx->sm_count};
     const int vec = dlspm_vec_width(N, B, C);
     const bool strict = ctx->strict_fp32 != 0;
-    const int split = spmm_row_split(ctx, M, N, nnz, vec, strict);
+    int split = spmm_row_split(ctx, M, N, nnz, vec, strict);
+    // Long rows of uneven length (known only with a plan): eight warps per row make every thread
+    // block finish its row together, which the binning by powers of two does not.  Measured on
+    // planned launches with a 40 % row-length spread and narrow slabs: mean length 1229: 178 -> 138 us,
+    // 2458: 614 -> 553 us, 819: 387 -> 357 us; at mean length 614 it went either way (2048 rows
+    // 48.7 -> 39.8 us, 8192 rows 131 -> 146 us), at 205 it lost 10 to 45 %, and with uniform rows it
+    // loses at every length, hence both conditions.
+    const double mean_len = (double)nnz / (double)M;
+    if (!strict && max_row_len > 0 && mean_len >= 800.0 && (double)max_row_len >= 1.3 * mean_len &&
+        spmm_slab_chunks(N, vec) <= 2)
+        split = 8;
     // narrow N: several rows per warp, but never so many that the matrix yields too few warps
     int lanes = 32;
     if (vec == 4 && N <= 64 && split == 1) {
@@ -263,7 +274,7 @@ extern "C" int dlspm_spmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, 
     if (rc) return rc;
     rc = dlspm_use(ctx);
     if (rc) return rc;
-    return spmm_launch(ctx, M, N, nnz, values, row_offsets, column_indices, B, C, nullptr,
+    return spmm_launch(ctx, M, N, nnz, values, row_offsets, column_indices, B, C, nullptr, 0,
                        (cudaStream_t)stream);
 }
 
@@ -278,7 +289,7 @@ extern "C" int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan
     rc = dlspm_use(ctx);
     if (rc) return rc;
     return spmm_launch(ctx, plan->M, N, plan->nnz, values, row_offsets, column_indices, B, C, plan->row_order,
-                       (cudaStream_t)stream);
+                       plan->max_row_len, (cudaStream_t)stream);
 }
 
 // ---- SpMM whose result rows go to several destinations (fused compute + gather) -----------------

@@ -292,3 +292,14 @@ def test_strict_mode_keeps_csr_order_with_batched_loads(pkg, oracle, ctx, dev):
             assert np.array_equal(out.view(np.uint32), ref.view(np.uint32)), N
     finally:
         ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+
+
+def test_planned_launch_with_long_uneven_rows(pkg, oracle, ctx, dev):
+    """A plan knows the longest row; long rows of uneven length then run with eight warps per row."""
+    M, K, N = 96, 4000, 128
+    ro, ci = csr_rowlen_normal(pkg, M, K, 0.7, 71)  # mean 1200, spread 40 %
+    vals = pkg.gen_dense_host(int(ci.size), 71, 2)
+    B = dense(pkg, K, N, 71, 10)
+    assert np.diff(ro).max() >= 1.3 * np.diff(ro).mean() >= 1.3 * 800
+    out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B, plan=True)
+    check(oracle, ro, ci, vals, B, M, N, out)
