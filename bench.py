@@ -123,30 +123,86 @@ class DeviceBatch:
         self.batch = ctx.batch_create(self.problems)
 
     def host_sample(self, max_bytes: int, max_problems: int):
-        """Pinned host copies of the first problems of this rank (inputs) plus pinned outputs."""
+        """Pinned host copies of the first problems of this rank: all inputs in ONE pinned arena in
+        the order and spacing of the library's staging layout (per problem row_offsets,
+        column_indices, values, B, each padded to 256 bytes), all outputs in a second one, so that
+        dlspm_spmm_batched_f32_host can send every 128 MiB piece with one copy per direction."""
         import torch
 
-        arr_items = []
-        total = 0
-        for (M, K, N, sp, pseed, ro), (o_ro, o_ci, o_v, o_B, o_C, nnz) in zip(self.items, self.layout):
+        def pad(nbytes):
+            return (nbytes + 255) // 256 * 256
+
+        picked, total, in_bytes, out_bytes = [], 0, 0, 0
+        for idx, ((M, K, N, sp, pseed, ro), lay) in enumerate(zip(self.items, self.layout)):
+            nnz = lay[5]
             b = spmm_bytes(M, K, N, nnz)
-            if arr_items and (total + b > max_bytes or len(arr_items) >= max_problems):
+            if picked and (total + b > max_bytes or len(picked) >= max_problems):
                 break
             total += b
-            h_ro = self.rpool[o_ro:o_ro + M + 1].cpu().pin_memory()
-            h_ci = self.ipool[o_ci:o_ci + nnz].cpu().pin_memory()
-            h_v = self.fpool[o_v:o_v + nnz].cpu().pin_memory()
-            h_B = self.fpool[o_B:o_B + K * N].cpu().pin_memory()
-            h_C = torch.empty(M * N, dtype=torch.float32).pin_memory()
-            arr_items.append((M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C))
-        arr = self.pkg.ProblemArray(len(arr_items))
+            offs = []
+            for nb in (4 * (M + 1), 4 * nnz, 4 * nnz, 4 * K * N):
+                offs.append(in_bytes)
+                in_bytes += pad(nb)
+            picked.append((idx, offs, out_bytes))
+            out_bytes += pad(4 * M * N)
+        arena_in = torch.empty(max(in_bytes, 256), dtype=torch.uint8).pin_memory()
+        arena_out = torch.empty(max(out_bytes, 256), dtype=torch.uint8).pin_memory()
+        in_i32, in_f32 = arena_in.view(torch.int32), arena_in.view(torch.float32)
+        base_in, base_out = arena_in.data_ptr(), arena_out.data_ptr()
+        arr = self.pkg.ProblemArray(len(picked))
         flops = h2d = d2h = 0.0
-        for i, (M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C) in enumerate(arr_items):
-            arr.set(i, M, K, N, nnz, h_v, h_ro, h_ci, h_B, h_C, host=True)
+        for i, (idx, (a_ro, a_ci, a_v, a_B), a_C) in enumerate(picked):
+            M, K, N, sp, pseed, ro = self.items[idx]
+            o_ro, o_ci, o_v, o_B, o_C, nnz = self.layout[idx]
+            in_i32[a_ro // 4:a_ro // 4 + M + 1].copy_(self.rpool[o_ro:o_ro + M + 1])
+            if nnz:
+                in_i32[a_ci // 4:a_ci // 4 + nnz].copy_(self.ipool[o_ci:o_ci + nnz])
+                in_f32[a_v // 4:a_v // 4 + nnz].copy_(self.fpool[o_v:o_v + nnz])
+            in_f32[a_B // 4:a_B // 4 + K * N].copy_(self.fpool[o_B:o_B + K * N])
+            arr.set_raw(i, M, K, N, nnz, base_in + a_v if nnz else None, base_in + a_ro,
+                        base_in + a_ci if nnz else None, base_in + a_B, base_out + a_C)
             flops += 2.0 * nnz * N
             h2d += 4 * (M + 1) + 8 * nnz + 4 * K * N
             d2h += 4 * M * N
-        return arr, arr_items, flops, h2d, d2h
+        torch.cuda.synchronize()
+        return arr, (arena_in, arena_out, picked), flops, h2d, d2h
+
+
+# ---- parity of the timed launch (outside the timed region) -----------------------------------------------------
+
+PARITY_TOL = 1e-4  # the tolerance of the parity tests: |out - ref| <= tol * max(|ref|, sum |products|)
+
+
+def parity_sample(pkg, oracle, batch, max_problems=90):
+    """Checks what the timed launch left in C against the CPU oracle, for one problem of every
+    distinct (shape, sparsity, width) combination of this rank's share (the batch has 90): the
+    inputs are regenerated on the host from the seeds (same bits as the device generators), the
+    output is copied back from the pool the timed launch wrote."""
+    threads = oracle.max_threads()
+    seen, picks = set(), []
+    for idx, (M, K, N, sp, pseed, ro) in enumerate(batch.items):
+        if (M, K, N, sp) not in seen:
+            seen.add((M, K, N, sp))
+            picks.append(idx)
+    if len(picks) > max_problems:
+        picks = [picks[i * len(picks) // max_problems] for i in range(max_problems)]
+    violations, worst, elements = 0, 0.0, 0
+    for idx in picks:
+        M, K, N, sp, pseed, ro = batch.items[idx]
+        o_ro, o_ci, o_v, o_B, o_C, nnz = batch.layout[idx]
+        ci = pkg.gen_sample_columns_host(M, K, ro, pseed)
+        vals = pkg.gen_dense_host(int(ci.size), pseed, 2)
+        B = pkg.gen_dense_host(K * N, pseed, 10).reshape(K, N)
+        out = batch.fpool[o_C:o_C + M * N].cpu().numpy().reshape(M, N)
+        ref = oracle.spmm(vals, ro, ci, B, M, N, threads=max(threads, 2))
+        scale = oracle.spmm_scale(vals, ro, ci, B, M, N, threads=max(threads, 2))
+        bad, w = oracle.violations(ref, out, scale, PARITY_TOL)
+        violations += int(bad)
+        worst = max(worst, min(float(w), 1e30))
+        elements += M * N
+    return {"checked": len(picks), "violations": violations, "elements": elements, "worst_ratio_of_tol": worst / PARITY_TOL if PARITY_TOL else None,
+            "tol": PARITY_TOL, "against": "CPU oracle (the reference's host loop), inputs regenerated from the seeds",
+            "what": "C of the timed grouped launch, one problem per distinct (shape, sparsity, N) of rank 0's share"}
 
 
 # ---- clocks ------------------------------------------------------------------------------------------------
@@ -202,6 +258,26 @@ class ClockSampler:
         if sm:
             out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
+
+
+def host_memory_available() -> float:
+    """Bytes of host memory this process may still use: MemAvailable, capped by the cgroup limit."""
+    avail = 64e9
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable:"):
+                avail = float(line.split()[1]) * 1024.0
+    except OSError:
+        pass
+    for path, used in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                       ("/sys/fs/cgroup/memory/memory.limit_in_bytes", "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            lim = open(path).read().strip()
+            if lim != "max":
+                avail = min(avail, float(lim) - float(open(used).read().strip()))
+        except (OSError, ValueError):
+            pass
+    return max(avail, 1e9)
 
 
 def measured_peaks():
@@ -605,6 +681,53 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
     return out
 
 
+_M64 = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def _mix64_np(z):
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def bernoulli_row_host(pkg, K, row, density, seed):
+    """Columns of one row of the Bernoulli pattern of `seed`, computed on the host with the
+    library's counter-based generator restated in numpy (checked against dlspm_rand_u64)."""
+    key = _mix64((seed + 0x9E3779B97F4A7C15) & _M64) ^ _mix64((1 * 0xD1342543DE82EF95 + 0x2545F4914F6CDD1D) & _M64)
+    with np.errstate(over="ignore"):
+        idx = np.uint64(row) * np.uint64(K) + np.arange(K, dtype=np.uint64)
+        h = _mix64_np(np.uint64(key) + (idx + np.uint64(1)) * np.uint64(0x9E3779B97F4A7C15))
+    assert int(h[0]) == pkg.rand_u64(seed, 1, row * K) and int(h[-1]) == pkg.rand_u64(seed, 1, row * K + K - 1)
+    thr = 0 if density <= 0 else (1 << 24) if density >= 1 else int(density * 16777216.0)
+    return np.nonzero((h >> np.uint64(40)) < np.uint64(thr))[0].astype(np.int32)
+
+
+def rowshard_reference_rows(pkg, oracle, K, N, density, seed, ro_all, rows):
+    """Oracle result (and tolerance magnitudes) of the sampled global rows of the row-sharded SpMM,
+    from inputs regenerated on the host: pattern rows, their values by CSR position, and all of B."""
+    cols, vals, lens = [], [], []
+    for r in rows:
+        c = bernoulli_row_host(pkg, K, int(r), density, seed)
+        assert c.size == int(ro_all[r + 1] - ro_all[r]), "row length differs from the device generator's"
+        cols.append(c)
+        vals.append(pkg.gen_dense_host(int(c.size), seed, 2, first_index=int(ro_all[r])))
+        lens.append(c.size)
+    ro = np.zeros(len(rows) + 1, dtype=np.int32)
+    ro[1:] = np.cumsum(lens)
+    ci = np.concatenate(cols) if cols else np.zeros(0, np.int32)
+    v = np.concatenate(vals) if vals else np.zeros(0, np.float32)
+    Bh = pkg.gen_dense_host(K * N, seed, 10).reshape(K, N)
+    ref = oracle.spmm(v, ro, ci, Bh, len(rows), N)
+    scale = oracle.spmm_scale(v, ro, ci, Bh, len(rows), N)
+    return ref, scale
+
+
 def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
     """One 65536 x 65536 SpMM at 1 % density, N = 512, rows sharded by nonzeros, C blocks gathered."""
     import torch
@@ -666,38 +789,67 @@ def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
                            "gflops": flops / ms * 1e-6},
            "nnz": total_nnz, "n_gpus": world}
     best_ms = ms
+    # oracle check of sampled rows (spread over every rank's block), inputs regenerated on the host
+    oracle = entry.load_oracle()
+    sample_rows = np.unique(np.linspace(0, M - 1, 96).astype(np.int64))
+    ref_rows, scale_rows = rowshard_reference_rows(pkg, oracle, K, N, density, seed, ro_all, sample_rows)
+    rows_t = torch.from_numpy(sample_rows).to(dev)
+
+    def violations_of(full_c):
+        got = full_c.index_select(0, rows_t).cpu().numpy()
+        bad, _w = oracle.violations(ref_rows, got, scale_rows, PARITY_TOL)
+        v = torch.tensor([int(bad)], device=dev, dtype=torch.int64)
+        if world > 1:
+            dist.all_reduce(v, op=dist.ReduceOp.SUM)
+        return int(v[0])
+
+    full_nccl = step()
+    torch.cuda.synchronize()
+    out["nccl_gather"]["oracle_rows_checked_per_rank"] = int(sample_rows.size)
+    out["nccl_gather"]["oracle_violations_all_ranks"] = violations_of(full_nccl.view(M, N))
     if world > 1:
         # fused form: the SpMM epilogue stores every row into the full C of all ranks over NVLink
         # (peer mappings through CUDA IPC), so no collective follows the kernel
         full_ptr, handle = ctx.peer_alloc(M * N * 4)
         handles = [None] * world
         dist.all_gather_object(handles, handle)
-        peers = [ctx.peer_open(h) for r, h in enumerate(handles) if r != rank]
-        dsts = [full_ptr] + peers
-        gathered = step()
-        for _ in range(2):
-            ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dsts, r0)
-        torch.cuda.synchronize()
-        dist.barrier()
-        ftimes = []
-        for _ in range(reps):
-            dist.barrier()
+        opened = {r: ctx.peer_open(h) for r, h in enumerate(handles) if r != rank}
+        peers = list(opened.values())
+        # destinations in ring order starting with this rank: at every step of the kernel's round of
+        # destinations the ranks then store to different GPUs
+        dsts = [full_ptr if (rank + j) % world == rank else opened[(rank + j) % world] for j in range(world)]
+        gathered = full_nccl
+
+        def time_scatter(dst_list):
+            for _ in range(2):
+                ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dst_list, r0)
             torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dsts, r0)
-            e1.record()
-            e1.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ftimes.append(float(t[0]))
-        dist.barrier()
+            dist.barrier()
+            ts = []
+            for _ in range(reps):
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ctx.spmm_scatter(rows, K, N, nnz, vals, ro, ci, B, dst_list, r0)
+                e1.record()
+                e1.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ts.append(float(t[0]))
+            dist.barrier()
+            return statistics.median(ts)
+
+        local_only_ms = time_scatter([full_ptr])  # same kernel, own C only: what the remote stores add
+        fms = time_scatter(dsts)
         mine = pkg.DeviceArray(full_ptr, (M, N)).tensor(dev)
-        same = torch.tensor([1 if torch.equal(mine, gathered) else 0], device=dev)
+        same = torch.tensor([1 if torch.equal(mine, gathered.view(M, N)) else 0], device=dev)
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
-        fms = statistics.median(ftimes)
         out["fused_peer_stores"] = {"ms_total_median": fms, "gflops": flops / fms * 1e-6,
-                                    "equals_nccl_result_on_every_rank": bool(int(same[0]))}
+                                    "ms_one_destination": local_only_ms,
+                                    "equals_nccl_result_on_every_rank": bool(int(same[0])),
+                                    "oracle_rows_checked_per_rank": int(sample_rows.size),
+                                    "oracle_violations_all_ranks": violations_of(mine)}
         best_ms = min(best_ms, fms)
         del mine, gathered
         torch.cuda.synchronize()
@@ -711,6 +863,19 @@ def run_rowshard(pkg, ctx, dev, rank, world, hbm_gbs, fp32_tflops, reps=5):
                 "hbm_frac": nbytes / best_ms * 1e-6 / (hbm_gbs * world),
                 "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / best_ms / world})
     return out
+
+
+def rowshard_summary(r):
+    """The figures of the row-sharded large SpMM in a few numbers (kept near the front of the line)."""
+    if not r:
+        return None
+    f = r.get("fused_peer_stores") or {}
+    g = r.get("nccl_gather") or {}
+    return {"n_gpus": r.get("n_gpus"), "ms": r.get("ms_total_median"), "ms_nccl_form": g.get("ms_total_median"),
+            "ms_kernel_only": g.get("ms_kernel_median"), "ms_fused_form": f.get("ms_total_median"),
+            "ms_fused_one_destination": f.get("ms_one_destination"),
+            "oracle_violations": (g.get("oracle_violations_all_ranks", 0) or 0) + (f.get("oracle_violations_all_ranks", 0) or 0),
+            "oracle_rows_per_rank": g.get("oracle_rows_checked_per_rank")}
 
 
 # ---- main arm ------------------------------------------------------------------------------------------------------
@@ -748,9 +913,10 @@ def main():
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed launch")
     ap.add_argument("--tile-density", type=int, default=None, help="DLSPM_OPT_TILE_MIN_DENSITY in thousandths")
     ap.add_argument("--spmm-kernel", type=int, default=0, help="0 auto, 1 row-gather only, 2 tiled where possible, 3 tiled with zeros")
-    ap.add_argument("--e2e-bytes", type=float, default=2e9, help="host bytes of the e2e sample per rank")
+    ap.add_argument("--e2e-bytes", type=float, default=16e9, help="host bytes of the e2e sample per rank")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -854,27 +1020,54 @@ def main():
                        "fp32_frac": fl / (ms * 1e-3) * 1e-12 / fp32_tflops}
     barrier()
 
+    # what the timed launches computed, against the CPU oracle (rank 0's share; after the timed
+    # region, so the check costs the measurement nothing)
+    parity = None
+    if rank == 0 and not args.no_parity:
+        parity = parity_sample(pkg, entry.load_oracle(), batch)
+        log(f"[rank 0] parity: {parity['checked']} problems, {parity['violations']} violations, "
+            f"worst {parity['worst_ratio_of_tol']:.3f} of tolerance")
+    barrier()
+
     # end to end through the host-buffer entry point (copies inside the timed region)
-    arr, keep, e_flops, e_h2d, e_d2h = batch.host_sample(int(args.e2e_bytes), 4096)
+    # the sample is bounded by the host memory the ranks of this machine can pin together
+    e_bytes = min(float(args.e2e_bytes), 0.35 * host_memory_available() / max(world, 1))
+    arr, keep, e_flops, e_h2d, e_d2h = batch.host_sample(int(e_bytes), 1 << 20)
+    n_sample = len(keep[2])
     e_steps = max(3, min(args.steps, 5))
     ctx.spmm_batched_host(arr)
     barrier()
+    copies0 = ctx.host_copy_count()
     t0 = time.perf_counter()
     for _ in range(e_steps):
         ctx.spmm_batched_host(arr)
     torch.cuda.synchronize()
     e_dt = (time.perf_counter() - t0) / e_steps
+    copies_per_step = (ctx.host_copy_count() - copies0) / e_steps
+    # what came back to the host is what the device-resident launch computed (same kernel, same bits)
+    out_f32 = keep[1].view(torch.float32)
+    e_same = True
+    for (idx, _offs, a_C) in keep[2][:: max(1, n_sample // 16)]:
+        M, K, N = batch.items[idx][:3]
+        o_C = batch.layout[idx][4]
+        e_same = e_same and bool(torch.equal(out_f32[a_C // 4:a_C // 4 + M * N], batch.fpool[o_C:o_C + M * N].cpu()))
     et = torch.tensor([e_dt], device=dev, dtype=torch.float64)
-    ef = torch.tensor([e_flops, e_h2d, e_d2h], device=dev, dtype=torch.float64)
+    ef = torch.tensor([e_flops, e_h2d, e_d2h, 1.0 if e_same else 0.0], device=dev, dtype=torch.float64)
+    emin = ef[3:4].clone()
     if world > 1:
         dist.all_reduce(et, op=dist.ReduceOp.MAX)
         dist.all_reduce(ef, op=dist.ReduceOp.SUM)
+        dist.all_reduce(emin, op=dist.ReduceOp.MIN)
     e2e = {"value": float(ef[0]) / float(et[0]) * 1e-9, "unit": "GFLOP/s",
            "h2d_bytes_per_step": float(ef[1]), "d2h_bytes_per_step": float(ef[2]),
-           "sample": f"first {len(keep)} problems of every rank's share, pinned host buffers, "
-                     "dlspm_spmm_batched_f32_host (H2D + grouped launch + D2H per step)",
-           "ms_per_step": float(et[0]) * 1e3}
-    del arr, keep
+           "sample": f"first {n_sample} problems of every rank's share (rank 0's count), inputs in one pinned arena and "
+                     "outputs in another, dlspm_spmm_batched_f32_host (H2D + grouped launch + D2H per step)",
+           "ms_per_step": float(et[0]) * 1e3,
+           "h2d_gbs_per_rank": float(ef[1]) / world / float(et[0]) * 1e-9,
+           "d2h_gbs_per_rank": float(ef[2]) / world / float(et[0]) * 1e-9,
+           "memcpy_calls_per_step_rank0": copies_per_step,
+           "results_equal_device_resident_launch": bool(float(emin[0]) > 0.5)}
+    del arr, keep, out_f32
 
     extras = {}
     if not args.no_extras:
@@ -898,8 +1091,9 @@ def main():
             "metric": "spmm_batch_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "rowshard_65536_summary": rowshard_summary(extras.get("rowshard_65536")),
             "data": "synthetic", "config": workload_config(args, world),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * launches_per_step,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "parity": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
                          "frac": achieved / hbm_gbs,
                          "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE[dominant] * dom["algorithmic_bytes_per_launch"]
@@ -929,6 +1123,8 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     ctx.close()
+    if parity is not None and parity["violations"]:
+        raise SystemExit(f"parity check failed: {parity['violations']} elements beyond tolerance")
 
 
 if __name__ == "__main__":

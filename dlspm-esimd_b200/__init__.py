@@ -108,6 +108,7 @@ _SIGNATURES = {
     "dlspm_mg_spmm_batched_f32_host": (_I, [_P, _I, C.POINTER(Problem)]),
     "dlspm_mg_spmm_rowshard_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "dlspm_measure_fp32_peak": (_I, [_P, C.POINTER(C.c_double)]),
+    "dlspm_host_copy_count": (_I, [_P, C.POINTER(C.c_longlong)]),
     "dlspm_selftest_bounded_wait": (_I, [_P, C.c_uint, C.POINTER(_I)]),
     "dlspm_spmm_csr_f32_scatter": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _I, C.POINTER(_P), C.c_longlong, _P]),
     "dlspm_enable_peer_access": (_I, [_P, _I]),
@@ -349,6 +350,12 @@ class Context:
     def spmm_batched_host(self, problems: "ProblemArray") -> None:
         _check(self.lib.dlspm_spmm_batched_f32_host(self.handle, len(problems), problems.array),
                "dlspm_spmm_batched_f32_host", self)
+
+    def host_copy_count(self) -> int:
+        """cudaMemcpyAsync calls issued so far by spmm_batched_host on this context."""
+        v = C.c_longlong()
+        _check(self.lib.dlspm_host_copy_count(self.handle, C.byref(v)), "dlspm_host_copy_count", self)
+        return v.value
 
     # device generators
     def gen_dense(self, out, seed, stream_id, first_index=0, kind=KIND_UNIFORM_PM1, stream=None) -> None:

@@ -32,6 +32,7 @@ struct dlspm_ctx {
     int pipeline_ready;
     void *pinned;  // pinned host memory for the launch tables of the pipelined batch
     size_t pinned_bytes;
+    long long host_copies;  // cudaMemcpyAsync calls issued by the pipelined host-buffer batch so far
 };
 
 struct dlspm_plan {

@@ -25,9 +25,27 @@ struct Carver {
 
 inline size_t padded(size_t bytes) { return (bytes + 255) & ~(size_t)255; }
 
+// A host-buffer call that fails half-way may still have copies and kernels in flight that read the
+// staging memory or write the caller's buffers.  Every such call therefore leaves through here: on
+// an error the streams it used are drained before the error is reported, so that when the call
+// returns nothing of it is running any more.
+int drain_on_error(dlspm_ctx *ctx, int rc)
+{
+    if (rc == DLSPM_OK || !ctx) return rc;
+    if (cudaSetDevice(ctx->device) == cudaSuccess) {
+        if (ctx->stream) (void)cudaStreamSynchronize(ctx->stream);
+        if (ctx->pipeline_ready) {
+            (void)cudaStreamSynchronize(ctx->h2d_stream);
+            (void)cudaStreamSynchronize(ctx->d2h_stream);
+        }
+    }
+    (void)cudaGetLastError();
+    return rc;
+}
+
 }  // namespace
 
-extern "C" int dlspm_spmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+static int dlspm_spmm_csr_f32_host_impl(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
                                        const int *row_offsets, const int *column_indices, const float *B,
                                        float *C)
 {
@@ -61,7 +79,7 @@ extern "C" int dlspm_spmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int 
     return DLSPM_OK;
 }
 
-extern "C" int dlspm_sddmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+static int dlspm_sddmm_csr_f32_host_impl(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
                                         const int *column_indices, const float *lhs, const float *rhs,
                                         float *out_values)
 {
@@ -93,7 +111,7 @@ extern "C" int dlspm_sddmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int
     return DLSPM_OK;
 }
 
-extern "C" int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+static int dlspm_fused_sddmm_spmm_f32_host_impl(dlspm_ctx *ctx, int M, int K, int N, int nnz,
                                                const int *row_offsets, const int *column_indices,
                                                const float *C, const float *B, const float *D, float *E)
 {
@@ -137,6 +155,95 @@ extern "C" int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int
 // piece still waits for its turn on the outbound stream.
 namespace {
 
+// Copies between host and device arrays that merge neighbours into one cudaMemcpyAsync.  Two arrays
+// are neighbours when the distance between their host addresses equals the distance between their
+// device addresses (the staging layout packs arrays at 256-byte boundaries in call order) and both
+// lie in ONE host allocation known to the driver (one cudaHostAlloc / cudaHostRegister range), so
+// that the few padding bytes between them are readable and the whole run is pinned.  A caller that
+// keeps its batch in one pinned arena in the staging order (per problem: row_offsets,
+// column_indices, values, B, each padded to 256 bytes; results likewise in a second arena) gets one
+// copy per 128 MiB piece and direction; any other layout is copied array by array as before.
+class RunCopier {
+public:
+    RunCopier(dlspm_ctx *ctx, cudaStream_t st, bool to_device) : ctx_(ctx), st_(st), to_device_(to_device) {}
+
+    int add(void *dev, const void *host, size_t bytes)
+    {
+        if (bytes == 0) return DLSPM_OK;
+        char *d = (char *)dev;
+        const char *h = (const char *)host;
+        if (run_bytes_ && d >= run_d_ + run_bytes_ && (size_t)(d - (run_d_ + run_bytes_)) < 256 &&
+            h == run_h_ + (d - run_d_) && same_host_range(run_h_, h + bytes)) {
+            run_bytes_ = (size_t)(d - run_d_) + bytes;
+            return DLSPM_OK;
+        }
+        int rc = flush();
+        if (rc) return rc;
+        run_d_ = d;
+        run_h_ = h;
+        run_bytes_ = bytes;
+        return DLSPM_OK;
+    }
+
+    int flush()
+    {
+        if (!run_bytes_) return DLSPM_OK;
+        const size_t n = run_bytes_;
+        run_bytes_ = 0;
+        copies_++;
+        if (to_device_) DLSPM_CUDA_TRY(ctx_, cudaMemcpyAsync(run_d_, run_h_, n, cudaMemcpyHostToDevice, st_));
+        else DLSPM_CUDA_TRY(ctx_, cudaMemcpyAsync(const_cast<char *>(run_h_), run_d_, n, cudaMemcpyDeviceToHost, st_));
+        return DLSPM_OK;
+    }
+
+    long long copies() const { return copies_; }
+
+private:
+    // CUresult cuPointerGetAttribute(void *data, CUpointer_attribute attribute, CUdeviceptr ptr)
+    typedef int (*PtrAttrFn)(void *, int, unsigned long long);
+
+    static PtrAttrFn driver_query()
+    {
+        static PtrAttrFn fn = []() -> PtrAttrFn {
+            void *p = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &p, cudaEnableDefault, &q) != cudaSuccess ||
+                q != cudaDriverEntryPointSuccess) {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            return (PtrAttrFn)p;
+        }();
+        return fn;
+    }
+
+    // true when [a, b) lies inside one host allocation registered with the driver
+    bool same_host_range(const char *a, const char *b)
+    {
+        if (a >= range_lo_ && b <= range_hi_) return true;
+        PtrAttrFn fn = driver_query();
+        if (!fn) return false;
+        unsigned long long start = 0;
+        size_t size = 0;
+        const int kRangeStart = 11, kRangeSize = 12;  // CU_POINTER_ATTRIBUTE_RANGE_START_ADDR / _RANGE_SIZE
+        if (fn(&start, kRangeStart, (unsigned long long)(uintptr_t)a) != 0 ||
+            fn(&size, kRangeSize, (unsigned long long)(uintptr_t)a) != 0)
+            return false;  // pageable or unknown memory: never merged
+        range_lo_ = (const char *)(uintptr_t)start;
+        range_hi_ = range_lo_ + size;
+        return a >= range_lo_ && b <= range_hi_;
+    }
+
+    dlspm_ctx *ctx_;
+    cudaStream_t st_;
+    bool to_device_;
+    char *run_d_ = nullptr;
+    const char *run_h_ = nullptr;
+    size_t run_bytes_ = 0;
+    const char *range_lo_ = nullptr, *range_hi_ = nullptr;
+    long long copies_ = 0;
+};
+
 int pipeline_init(dlspm_ctx *ctx)
 {
     if (ctx->pipeline_ready) return DLSPM_OK;
@@ -153,7 +260,7 @@ int pipeline_init(dlspm_ctx *ctx)
 
 }  // namespace
 
-extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_problem *problems)
+static int dlspm_spmm_batched_f32_host_impl(dlspm_ctx *ctx, int count, const dlspm_problem *problems)
 {
     if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
@@ -216,8 +323,11 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
             DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(h2d, ctx->ev_d2h[b], 0));
             DLSPM_CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev_kernel[b]));
         }
+        // staging layout of a piece: the inputs of all its problems first (per problem row_offsets,
+        // column_indices, values, B), then all results, every array at a 256-byte boundary
         Carver cv(base + padded(max_tables));
         dev[b].clear();
+        RunCopier in(ctx, h2d, true);
         for (int i = first; i < last; i++) {
             const dlspm_problem &q = problems[i];
             dlspm_problem d = q;
@@ -225,20 +335,24 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
             int *d_ci = cv.take<int>((size_t)q.nnz);
             float *d_v = cv.take<float>((size_t)q.nnz);
             float *d_B = cv.take<float>((size_t)q.K * q.N);
-            float *d_C = cv.take<float>((size_t)q.M * q.N);
-            DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ro, q.row_offsets, 4 * ((size_t)q.M + 1), cudaMemcpyHostToDevice, h2d));
-            if (q.nnz) {
-                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_ci, q.column_indices, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, h2d));
-                DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, q.values, 4 * (size_t)q.nnz, cudaMemcpyHostToDevice, h2d));
-            }
-            if ((size_t)q.K * q.N > 0) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_B, q.B, 4 * (size_t)q.K * q.N, cudaMemcpyHostToDevice, h2d));
+            rc = in.add(d_ro, q.row_offsets, 4 * ((size_t)q.M + 1));
+            if (!rc) rc = in.add(d_ci, q.column_indices, 4 * (size_t)q.nnz);
+            if (!rc) rc = in.add(d_v, q.values, 4 * (size_t)q.nnz);
+            if (!rc) rc = in.add(d_B, q.B, 4 * (size_t)q.K * q.N);
+            if (rc) return rc;
             d.row_offsets = d_ro;
             d.column_indices = d_ci;
             d.values = d_v;
             d.B = d_B;
-            d.C = d_C;
             dev[b].push_back(d);
         }
+        rc = in.flush();
+        if (rc) return rc;
+        for (int i = first; i < last; i++) {
+            const dlspm_problem &q = problems[i];
+            dev[b][(size_t)(i - first)].C = cv.take<float>((size_t)q.M * q.N);
+        }
+        ctx->host_copies += in.copies();
         DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_h2d[b], h2d));
         DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(run, ctx->ev_h2d[b], 0));
         rc = dlspm_spmm_batched_at(ctx, (int)dev[b].size(), dev[b].data(), base, run,
@@ -246,16 +360,54 @@ extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlsp
         if (rc) return rc;
         DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_kernel[b], run));
         DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(d2h, ctx->ev_kernel[b], 0));
+        RunCopier outc(ctx, d2h, false);
         for (int i = first; i < last; i++) {
             const dlspm_problem &q = problems[i];
-            const size_t nC = (size_t)q.M * q.N;
-            if (nC) DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(q.C, dev[b][(size_t)(i - first)].C, 4 * nC, cudaMemcpyDeviceToHost, d2h));
+            rc = outc.add(dev[b][(size_t)(i - first)].C, q.C, 4 * (size_t)q.M * q.N);
+            if (rc) return rc;
         }
+        rc = outc.flush();
+        if (rc) return rc;
+        ctx->host_copies += outc.copies();
         DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_d2h[b], d2h));
         first = last;
     }
     DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(d2h));
     DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(run));
     DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(h2d));
+    return DLSPM_OK;
+}
+
+// ---- exported entry points: the implementations above plus the drain on failure ---------------------
+extern "C" int dlspm_spmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
+                                       const int *row_offsets, const int *column_indices, const float *B,
+                                       float *C)
+{
+    return drain_on_error(ctx, dlspm_spmm_csr_f32_host_impl(ctx, M, K, N, nnz, values, row_offsets, column_indices, B, C));
+}
+
+extern "C" int dlspm_sddmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                                        const int *column_indices, const float *lhs, const float *rhs,
+                                        float *out_values)
+{
+    return drain_on_error(ctx, dlspm_sddmm_csr_f32_host_impl(ctx, M, K, N, nnz, row_offsets, column_indices, lhs, rhs, out_values));
+}
+
+extern "C" int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
+                                               const int *row_offsets, const int *column_indices,
+                                               const float *C, const float *B, const float *D, float *E)
+{
+    return drain_on_error(ctx, dlspm_fused_sddmm_spmm_f32_host_impl(ctx, M, K, N, nnz, row_offsets, column_indices, C, B, D, E));
+}
+
+extern "C" int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_problem *problems)
+{
+    return drain_on_error(ctx, dlspm_spmm_batched_f32_host_impl(ctx, count, problems));
+}
+
+extern "C" int dlspm_host_copy_count(const dlspm_ctx *ctx, long long *copies)
+{
+    if (!ctx || !copies) return DLSPM_ERR_INVALID_ARGUMENT;
+    *copies = ctx->host_copies;
     return DLSPM_OK;
 }

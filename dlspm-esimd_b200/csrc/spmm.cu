@@ -308,7 +308,7 @@ struct ScatterArgs {
     int ndst;
 };
 
-template <int VEC, int U>
+template <int VEC, int U, bool STRICT>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(const ScatterArgs s)
 {
     __shared__ int2 stage[kWarpsPerCta][32];
@@ -349,15 +349,20 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(co
                     float b[VEC];
                     load_vec<VEC>(brow + cidx[u], b);
 #pragma unroll
-                    for (int v = 0; v < VEC; v++) acc[u][v] = fmaf(av, b[v], acc[u][v]);
+                    for (int v = 0; v < VEC; v++) acc[u][v] = mad<STRICT>(av, b[v], acc[u][v]);
                 }
             }
         }
         __syncwarp();
     }
     const size_t off = (size_t)(s.first_row + row) * (size_t)a.N;
+    // Every warp starts its round of destinations at another one, so that the warps of a GPU (and,
+    // when every GPU lists its destinations starting with itself in ring order, the GPUs among
+    // themselves) do not all store to the same peer at the same moment.
+    int dd = (int)((tile + warp) % s.ndst);
     for (int d = 0; d < s.ndst; d++) {
-        float *crow = s.dst[d] + off;
+        float *crow = s.dst[dd] + off;
+        if (++dd == s.ndst) dd = 0;
 #pragma unroll
         for (int u = 0; u < U; u++)
             if (cidx[u] < a.N) store_vec<VEC>(crow + cidx[u], acc[u]);
@@ -365,10 +370,12 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(co
 }
 
 template <int VEC, int U>
-void launch_scatter(const ScatterArgs &s, cudaStream_t st)
+void launch_scatter(const ScatterArgs &s, bool strict, cudaStream_t st)
 {
     const int slabs = dlspm_ceil_div(s.a.N, 32 * VEC * U);
-    spmm_rows_scatter_kernel<VEC, U><<<(unsigned)((long long)s.a.row_groups * slabs), kWarpsPerCta * 32, 0, st>>>(s);
+    const unsigned blocks = (unsigned)((long long)s.a.row_groups * slabs);
+    if (strict) spmm_rows_scatter_kernel<VEC, U, true><<<blocks, kWarpsPerCta * 32, 0, st>>>(s);
+    else spmm_rows_scatter_kernel<VEC, U, false><<<blocks, kWarpsPerCta * 32, 0, st>>>(s);
 }
 
 }  // namespace
@@ -398,18 +405,19 @@ extern "C" int dlspm_spmm_csr_f32_scatter(dlspm_ctx *ctx, int M, int K, int N, i
     const int vec = dlspm_vec_width(N, B, align_probe);
     const int U = spmm_slab_chunks(N, vec);
     cudaStream_t st = (cudaStream_t)stream;
+    const bool strict = ctx->strict_fp32 != 0;
     if (vec == 4) {
-        if (U == 4) launch_scatter<4, 4>(s, st);
-        else if (U == 2) launch_scatter<4, 2>(s, st);
-        else launch_scatter<4, 1>(s, st);
+        if (U == 4) launch_scatter<4, 4>(s, strict, st);
+        else if (U == 2) launch_scatter<4, 2>(s, strict, st);
+        else launch_scatter<4, 1>(s, strict, st);
     } else if (vec == 2) {
-        if (U == 4) launch_scatter<2, 4>(s, st);
-        else if (U == 2) launch_scatter<2, 2>(s, st);
-        else launch_scatter<2, 1>(s, st);
+        if (U == 4) launch_scatter<2, 4>(s, strict, st);
+        else if (U == 2) launch_scatter<2, 2>(s, strict, st);
+        else launch_scatter<2, 1>(s, strict, st);
     } else {
-        if (U == 4) launch_scatter<1, 4>(s, st);
-        else if (U == 2) launch_scatter<1, 2>(s, st);
-        else launch_scatter<1, 1>(s, st);
+        if (U == 4) launch_scatter<1, 4>(s, strict, st);
+        else if (U == 2) launch_scatter<1, 2>(s, strict, st);
+        else launch_scatter<1, 1>(s, strict, st);
     }
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;

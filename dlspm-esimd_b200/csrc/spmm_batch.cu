@@ -2,6 +2,7 @@
 // tiles from a device counter, the analysis of a batch (row order by length, sortedness), prepared
 // batches with the optional tiled kernel, the one-shot launch and the variant that allocates nothing.
 #include <algorithm>
+#include <atomic>
 #include <new>
 #include <vector>
 
@@ -86,6 +87,49 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
 
 namespace {
 
+// Table entry of one problem (natural row order).
+BatchProblem make_batch_problem(const dlspm_problem &q)
+{
+    BatchProblem b;
+    b.values = q.values;
+    b.row_offsets = q.row_offsets;
+    b.cols = q.column_indices;
+    b.B = q.B;
+    b.C = q.C;
+    b.M = q.M;
+    b.N = q.N;
+    b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+    b.vec = dlspm_vec_width(q.N, q.B, q.C);
+    b.chunks = spmm_slab_chunks(q.N, b.vec);
+    b.K = q.K;
+    b.row_order = nullptr;
+    b.nnz = q.nnz;
+    b.pad = 0;
+    return b;
+}
+
+// The one-shot grouped launches copy their tables from host memory that does not outlive the call,
+// so they cannot be recorded into a CUDA graph (a replay would read a dead buffer): on a capturing
+// stream they refuse before anything is enqueued.  Prepared batches (dlspm_batch_create +
+// dlspm_batch_launch) keep their tables on the device and are the form to capture.
+int reject_capturing_stream(dlspm_ctx *ctx, cudaStream_t st, const char *who)
+{
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    cudaError_t err = cudaStreamIsCapturing(st, &status);
+    if (err != cudaSuccess) {
+        // the legacy default stream cannot be queried while another stream of the thread captures
+        (void)cudaGetLastError();
+        status = cudaStreamCaptureStatusActive;
+    }
+    if (status != cudaStreamCaptureStatusNone) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "%s: the stream is being captured; one-shot grouped launches copy tables from host memory and cannot be "
+                 "recorded, use dlspm_batch_create + dlspm_batch_launch", who);
+        return DLSPM_ERR_UNSUPPORTED;
+    }
+    return DLSPM_OK;
+}
+
 // Builds the host-side tables for a batch: problems ordered by decreasing nnz*N.
 int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProblem> &tab,
                  std::vector<long long> &starts)
@@ -107,21 +151,7 @@ int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProb
     long long run = 0;
     for (int i : order) {
         const dlspm_problem &q = problems[i];
-        BatchProblem b;
-        b.values = q.values;
-        b.row_offsets = q.row_offsets;
-        b.cols = q.column_indices;
-        b.B = q.B;
-        b.C = q.C;
-        b.M = q.M;
-        b.N = q.N;
-        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
-        b.vec = dlspm_vec_width(q.N, q.B, q.C);
-        b.chunks = spmm_slab_chunks(q.N, b.vec);
-        b.K = q.K;
-        b.row_order = nullptr;
-        b.nnz = q.nnz;
-        b.pad = 0;
+        const BatchProblem b = make_batch_problem(q);
         starts.push_back(run);
         run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
         tab.push_back(b);
@@ -479,6 +509,8 @@ extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_pro
     int rc = dlspm_use(ctx);
     if (rc) return rc;
     if (count == 0) return DLSPM_OK;
+    rc = reject_capturing_stream(ctx, (cudaStream_t)stream, "dlspm_spmm_batched_f32");
+    if (rc) return rc;
     rc = dlspm_scratch_reserve(ctx, dlspm_batched_table_bytes(count));
     if (rc) return rc;
     return dlspm_spmm_batched_at(ctx, count, problems, ctx->scratch, (cudaStream_t)stream);
@@ -492,7 +524,7 @@ extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_pro
 // counter in context scratch that grows with cudaMalloc on demand; the variant below keeps them in
 // a fixed array that is part of the library image instead, so the call never allocates.  The price
 // is a hard limit on the batch size, and that every GPU which loads the library carries the array
-// (about 73 KiB) until the process exits.
+// (kStaticScratchBytes = 90 624 bytes, 88.5 KiB) until the process exits.
 namespace {
 
 constexpr int kStaticMaxProblems = 1024;
@@ -501,33 +533,44 @@ constexpr size_t kStaticStartsOff = (kStaticTableBytes + 255) & ~(size_t)255;
 constexpr size_t kStaticStartsBytes = sizeof(long long) * (kStaticMaxProblems + 1);
 constexpr size_t kStaticCounterOff = (kStaticStartsOff + kStaticStartsBytes + 255) & ~(size_t)255;
 constexpr size_t kStaticScratchBytes = kStaticCounterOff + 256;
+// the size quoted in the header and the documentation
+static_assert(sizeof(BatchProblem) == 80 && kStaticScratchBytes == 90624, "update the documented size of the static scratch");
 
 // Problem table, tile index and work counter of dlspm_spmm_batched_f32_static.  In host code this
 // name is only a handle for cudaGetSymbolAddress, never an address a kernel can use.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void *g_static_scratch_addr[kMaxDevices];  // device address of g_static_scratch, per device
-bool g_static_scratch_ready[kMaxDevices];
+// Device address of g_static_scratch per device (null until looked up).  Contexts on different host
+// threads may get here at the same time: the address is published with release/acquire ordering, and
+// two threads that both find it missing both look it up and store the same value.
+std::atomic<void *> g_static_scratch_addr[kMaxDevices];
 
 // Looks up the device address of the static scratch on the context's device (which is current),
 // once per device.
 int static_scratch_address(dlspm_ctx *ctx, unsigned char **out)
 {
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return DLSPM_ERR_UNSUPPORTED;
-    if (!g_static_scratch_ready[ctx->device]) {
-        void *p = nullptr;
+    void *p = g_static_scratch_addr[ctx->device].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t err = cudaGetSymbolAddress(&p, g_static_scratch);
         if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaGetSymbolAddress(g_static_scratch)");
-        g_static_scratch_addr[ctx->device] = p;
-        g_static_scratch_ready[ctx->device] = true;
+        g_static_scratch_addr[ctx->device].store(p, std::memory_order_release);
     }
-    *out = (unsigned char *)g_static_scratch_addr[ctx->device];
+    *out = (unsigned char *)p;
     return DLSPM_OK;
 }
 
+constexpr int kStaticChunk = 32;  // table entries built on the stack and copied at a time
+
 }  // namespace
 
+// Host memory: none from the heap, and about 5 KiB of stack (a 2 KiB order array of 16-bit indices
+// and one chunk of kStaticChunk table entries), so the call also fits the small stacks of plug-in
+// and real-time threads.  The table is sent in chunks; every cudaMemcpyAsync here has a pageable
+// source of a few KiB, which the runtime copies out before it returns, so the chunk buffer can be
+// reused at once.  Because of these copies the call cannot be recorded into a CUDA graph: on a
+// capturing stream it returns DLSPM_ERR_UNSUPPORTED before anything is enqueued.
 extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                                              void *stream)
 {
@@ -540,57 +583,48 @@ extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dl
     }
     int rc = dlspm_use(ctx);
     if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = reject_capturing_stream(ctx, st, "dlspm_spmm_batched_f32_static");
+    if (rc) return rc;
     unsigned char *base = nullptr;
     rc = static_scratch_address(ctx, &base);
     if (rc) return rc;
 
-    // Host tables on the stack (no heap either): same order as the allocating entry point,
-    // decreasing nnz*N with the lower index first on ties.
-    BatchProblem tab[kStaticMaxProblems];
-    long long starts[kStaticMaxProblems + 1];
-    int order[kStaticMaxProblems];
+    // Same order as the allocating entry point: decreasing nnz*N, the lower index first on ties.
+    unsigned short order[kStaticMaxProblems];
     int used = 0;
     for (int i = 0; i < count; i++) {
         const dlspm_problem &q = problems[i];
         rc = check_spmm_args(q.M, q.K, q.N, q.nnz, q.values, q.row_offsets, q.column_indices, q.B, q.C);
         if (rc) return rc;
-        if (q.M > 0 && q.N > 0) order[used++] = i;
+        if (q.M > 0 && q.N > 0) order[used++] = (unsigned short)i;
     }
     if (used == 0) return DLSPM_OK;
-    std::sort(order, order + used, [&](int x, int y) {
+    std::sort(order, order + used, [&](unsigned short x, unsigned short y) {
         const double wx = (double)problems[x].nnz * problems[x].N, wy = (double)problems[y].nnz * problems[y].N;
         return wx != wy ? wx > wy : x < y;
     });
-    long long run = 0;
-    for (int s = 0; s < used; s++) {
-        const dlspm_problem &q = problems[order[s]];
-        BatchProblem &b = tab[s];
-        b.values = q.values;
-        b.row_offsets = q.row_offsets;
-        b.cols = q.column_indices;
-        b.B = q.B;
-        b.C = q.C;
-        b.M = q.M;
-        b.N = q.N;
-        b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
-        b.vec = dlspm_vec_width(q.N, q.B, q.C);
-        b.chunks = spmm_slab_chunks(q.N, b.vec);
-        b.K = q.K;
-        b.row_order = nullptr;
-        b.nnz = q.nnz;
-        b.pad = 0;
-        starts[s] = run;
-        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
-    }
-    starts[used] = run;
 
-    cudaStream_t st = (cudaStream_t)stream;
     BatchProblem *d_tab = (BatchProblem *)base;
     long long *d_starts = (long long *)(base + kStaticStartsOff);
     unsigned long long *d_counter = (unsigned long long *)(base + kStaticCounterOff);
     // The array keeps what the previous call left in it: the tables are overwritten here and the
     // work counter is cleared by batch_launch_tables before the kernel starts.
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_tab, tab, sizeof(BatchProblem) * (size_t)used, cudaMemcpyHostToDevice, st));
-    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_starts, starts, sizeof(long long) * ((size_t)used + 1), cudaMemcpyHostToDevice, st));
+    BatchProblem tab[kStaticChunk];
+    long long starts[kStaticChunk + 1];
+    long long run = 0;
+    for (int s0 = 0; s0 < used; s0 += kStaticChunk) {
+        const int n = std::min(kStaticChunk, used - s0);
+        for (int s = 0; s < n; s++) {
+            tab[s] = make_batch_problem(problems[order[s0 + s]]);
+            starts[s] = run;
+            run += (long long)tab[s].row_groups * dlspm_ceil_div(tab[s].N, 32 * tab[s].vec * tab[s].chunks);
+        }
+        const bool last = s0 + n == used;
+        if (last) starts[n] = run;
+        DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_tab + s0, tab, sizeof(BatchProblem) * (size_t)n, cudaMemcpyHostToDevice, st));
+        DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_starts + s0, starts, sizeof(long long) * (size_t)(n + (last ? 1 : 0)),
+                                            cudaMemcpyHostToDevice, st));
+    }
     return batch_launch_tables(ctx, d_tab, d_starts, d_counter, used, run, st);
 }

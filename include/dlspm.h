@@ -166,7 +166,11 @@ typedef struct dlspm_problem {
 
 /* Runs `count` independent SpMMs in one launch.  Replaces the per-matrix process launches of
  * the batch drivers (SPMM/batch-run-spmm_fromfile:29-47).  `problems` is a HOST array; the
- * table is copied to device scratch owned by the context. */
+ * table is copied to device scratch owned by the context, so calls on one context must be ordered
+ * on one stream (two calls whose work overlaps on the GPU would share that scratch).  The table
+ * copies read host memory that dies with the call, so the call cannot be recorded into a CUDA
+ * graph: on a capturing stream it returns DLSPM_ERR_UNSUPPORTED before anything is enqueued (use
+ * dlspm_batch_create + dlspm_batch_launch there). */
 int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                            void *stream);
 
@@ -174,11 +178,14 @@ int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *probl
  * owns the device heap, a loop that may not take the allocator's lock).  This entry point has no
  * counterpart in the reference.  It never calls cudaMalloc/cudaFree or any allocating routine: its
  * problem table, tile index and work counter live in a fixed __device__ array inside the library
- * (about 73 KiB per GPU, held until the process exits).  Limit: count <= 1024 problems, otherwise
- * DLSPM_ERR_UNSUPPORTED.  The first call on a device looks up the array's device address; make
- * that call before any stream capture.  All calls on a device share the one array, so two calls
- * whose work overlaps on the GPU (different streams, no ordering) race; calls on one stream are
- * safe.  Results are identical to dlspm_spmm_batched_f32. */
+ * (90 624 bytes = 88.5 KiB per GPU, held until the process exits).  Limit: count <= 1024 problems,
+ * otherwise DLSPM_ERR_UNSUPPORTED.  Host side: no heap either, and about 5 KiB of stack (the table is
+ * built and sent in chunks of 32 problems), so it fits the small stacks of plug-in threads.  The
+ * first call on a device looks up the array's device address; make that call before any stream
+ * capture starts in the process.  Like the allocating one-shot call it copies its table from host
+ * memory and therefore refuses a capturing stream with DLSPM_ERR_UNSUPPORTED.  All calls on a device
+ * share the one array, so two calls whose work overlaps on the GPU (different streams, no ordering)
+ * race; calls on one stream are safe.  Results are identical to dlspm_spmm_batched_f32. */
 int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                                   void *stream);
 
@@ -217,8 +224,17 @@ int dlspm_sddmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
 int dlspm_fused_sddmm_spmm_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz,
                                     const int *row_offsets, const int *column_indices,
                                     const float *C, const float *B, const float *D, float *E);
-/* Batched SpMM with host pointers inside every dlspm_problem. */
+/* Batched SpMM with host pointers inside every dlspm_problem: pieces of up to 128 MiB are copied in,
+ * run as one grouped launch and copied out on three streams, so the two copy directions and the
+ * kernels overlap.  Arrays are copied one by one unless they are neighbours in ONE pinned host
+ * allocation in the order and spacing of the staging layout (per problem row_offsets,
+ * column_indices, values, B, each padded to a multiple of 256 bytes, problems one after the other;
+ * the C buffers likewise in problem order): such a run goes as a single copy, one per piece and
+ * direction for a batch kept in two pinned arenas.  Results are the same either way. */
 int dlspm_spmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_problem *problems);
+/* Number of cudaMemcpyAsync calls the pipelined host-buffer batch has issued on this context so far
+ * (lets a caller see whether its buffer layout was merged into few copies). */
+int dlspm_host_copy_count(const dlspm_ctx *ctx, long long *copies);
 
 /* ---- .smtx reader and CSR validation (host) -------------------------------------------- */
 

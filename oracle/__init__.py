@@ -164,8 +164,13 @@ def fused_order(row_offsets, cols, c, b, d, M, N) -> np.ndarray:
     return e
 
 
-def spmm_scale(values, row_offsets, cols, B, M, N) -> np.ndarray:
+def spmm_scale(values, row_offsets, cols, B, M, N, threads: int = 1) -> np.ndarray:
+    """Sum of |products| behind every output element (the magnitude term of the tolerance).  With
+    threads > 1 it is formed as the fp32 product of |A| and |B| on all threads, which is accurate to
+    a few ulp: more than enough for a magnitude."""
     values, row_offsets, cols, B = _f32(values), _i32(row_offsets), _i32(cols), _f32(B)
+    if threads > 1:
+        return spmm(np.abs(values), row_offsets, cols, np.abs(B), M, N, threads=threads, fast_order=True)
     out = np.zeros((M, N), dtype=np.float32)
     lib().oracle_spmm_scale(_p(values), _p(row_offsets), _p(cols), _p(B), _p(out), M, N)
     return out

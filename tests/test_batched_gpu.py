@@ -128,6 +128,54 @@ def test_batched_host_with_pinned_memory(pkg, oracle, ctx):
     check_all(oracle, probs, [o.numpy() for o in outs])
 
 
+def test_batched_host_sends_one_pinned_arena_with_few_copies(pkg, oracle, ctx):
+    """Inputs kept in one pinned arena in the staging order and spacing (and outputs in another) go
+    as one copy per piece and direction; the same batch from separate arrays goes array by array;
+    both give the oracle's result."""
+    import torch
+
+    probs = make_problems(pkg, 30, seed=11, widths=(256, 100, 64, 1024))
+
+    def pad(nbytes):
+        return (nbytes + 255) // 256 * 256
+
+    in_bytes = sum(pad(4 * (M + 1)) + 2 * pad(4 * ci.size) + pad(4 * K * N) for (M, K, N, ro, ci, vals, B) in probs)
+    out_bytes = sum(pad(4 * M * N) for (M, K, N, *_r) in probs)
+    arena_in = torch.zeros(in_bytes, dtype=torch.uint8).pin_memory()
+    arena_out = torch.zeros(out_bytes, dtype=torch.uint8).pin_memory()
+    in_np, out_np = arena_in.numpy(), arena_out.numpy()
+    arr = pkg.ProblemArray(len(probs))
+    off, ooff, views = 0, 0, []
+    for i, (M, K, N, ro, ci, vals, B) in enumerate(probs):
+        ptrs = []
+        for a in (ro.astype(np.int32), ci.astype(np.int32), vals.astype(np.float32), B.astype(np.float32).ravel()):
+            in_np[off:off + a.nbytes] = a.view(np.uint8)
+            ptrs.append(arena_in.data_ptr() + off)
+            off += pad(a.nbytes)
+        nnz = int(ci.size)
+        arr.set_raw(i, M, K, N, nnz, ptrs[2] if nnz else None, ptrs[0], ptrs[1] if nnz else None, ptrs[3],
+                    arena_out.data_ptr() + ooff)
+        views.append((ooff, M * N))
+        ooff += pad(4 * M * N)
+    c0 = ctx.host_copy_count()
+    ctx.spmm_batched_host(arr)
+    assert ctx.host_copy_count() - c0 == 2, "one pinned arena per direction should be one copy each"
+    outs = [out_np[o:o + 4 * n].view(np.float32).copy() for (o, n) in views]
+    check_all(oracle, probs, outs)
+    # separate (pageable) arrays: copied one by one, same bits
+    arr2 = pkg.ProblemArray(len(probs))
+    outs2 = []
+    for i, (M, K, N, ro, ci, vals, B) in enumerate(probs):
+        o = np.full(M * N, np.nan, dtype=np.float32)
+        outs2.append(o)
+        arr2.set(i, M, K, N, int(ci.size), vals, ro, ci, np.ascontiguousarray(B).ravel(), o, host=True)
+    c0 = ctx.host_copy_count()
+    ctx.spmm_batched_host(arr2)
+    assert ctx.host_copy_count() - c0 > len(probs)
+    for a, b in zip(outs, outs2):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 def test_device_generators_match_host(pkg, ctx, dev):
     import torch
 

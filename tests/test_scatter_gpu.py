@@ -51,6 +51,25 @@ def test_scatter_writes_row_block_into_every_destination(pkg, oracle, ctx, dev, 
     assert torch.allclose(plain, dsts[0], rtol=1e-5, atol=1e-5)
 
 
+def test_scatter_strict_mode_reproduces_the_host_loop_bits(pkg, oracle, ctx, dev):
+    """With DLSPM_OPT_STRICT_FP32 the scatter form multiplies and adds with separate roundings in
+    CSR order, like dlspm_spmm_csr_f32: every destination holds the oracle's bits."""
+    import torch
+
+    M, K, N, ro, ci, vals, B = _case(pkg, M=300, K=200, N=132, seed=41)
+    dsts = [torch.full((M, N), float("nan"), device=dev) for _ in range(3)]
+    ctx.set_option(pkg.OPT_STRICT_FP32, 1)
+    try:
+        ctx.spmm_scatter(M, K, N, int(ci.size), to_dev(vals, dev), to_dev(ro, dev), to_dev(ci, dev), to_dev(B, dev),
+                         [d.data_ptr() for d in dsts], 0)
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+    ref = oracle.spmm(vals, ro, ci, B, M, N)
+    for d in dsts:
+        assert np.array_equal(d.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+
+
 def test_scatter_rejects_bad_destination_lists(pkg, ctx, dev):
     import torch
 

@@ -30,8 +30,10 @@ def run_spmm(ctx, dev, M, K, N, ro, ci, vals, B, plan=False, guard=64):
 
 
 def check(oracle, ro, ci, vals, B, M, N, out):
-    ref = oracle.spmm(vals, ro, ci, B, M, N)
-    scale = oracle.spmm_scale(vals, ro, ci, B, M, N)
+    big = float(ci.size) * N > 2e8  # large cases: the same loop with its rows spread over the host threads
+    threads = oracle.max_threads() if big else 1
+    ref = oracle.spmm(vals, ro, ci, B, M, N, threads=threads)
+    scale = oracle.spmm_scale(vals, ro, ci, B, M, N, threads=threads)
     assert not np.isnan(out).any(), "output not fully written"
     bad, worst = oracle.violations(ref, out, scale, TOL)
     assert bad == 0, f"{bad} elements beyond tolerance, worst ratio {worst:.3e}"
@@ -50,16 +52,57 @@ def test_dense_widths(pkg, oracle, ctx, dev, N):
     check(oracle, ro, ci, vals, B, M, N, run_spmm(ctx, dev, M, K, N, ro, ci, vals, B))
 
 
-@pytest.mark.parametrize("shape", [(64, 64), (256, 256), (512, 2048), (2048, 512), (1024, 4096)])
-@pytest.mark.parametrize("sparsity", [0.5, 0.9, 0.98])
-def test_sweep_shapes(pkg, oracle, ctx, dev, shape, sparsity):
-    M, K = shape
-    N = 256
-    seed = M * 7 + int(sparsity * 100)
+SWEEP_SHAPES = [(64, 64), (256, 256), (512, 2048), (2048, 512), (1024, 4096)]
+SWEEP_SPARSITIES = [0.5, 0.7, 0.8, 0.9, 0.95, 0.98]
+SWEEP_WIDTHS = [256, 1024, 3136]
+
+
+def sweep_case(pkg, M, K, N, sparsity):
+    seed = M * 7 + int(sparsity * 100) + N
     ro, ci = csr_rowlen_normal(pkg, M, K, sparsity, seed)
     vals = pkg.gen_dense_host(int(ci.size), seed, 2)
     B = dense(pkg, K, N, seed, 10)
+    return ro, ci, vals, B
+
+
+@pytest.mark.parametrize("N", SWEEP_WIDTHS)
+@pytest.mark.parametrize("shape", SWEEP_SHAPES)
+@pytest.mark.parametrize("sparsity", SWEEP_SPARSITIES)
+def test_sweep_shapes(pkg, oracle, ctx, dev, shape, sparsity, N):
+    """All 90 cases of the sweep configuration (5 shapes x 6 sparsities x 3 widths) at full size, as
+    lone launches."""
+    M, K = shape
+    ro, ci, vals, B = sweep_case(pkg, M, K, N, sparsity)
     check(oracle, ro, ci, vals, B, M, N, run_spmm(ctx, dev, M, K, N, ro, ci, vals, B))
+
+
+@pytest.mark.parametrize("kernel", [0, 2])
+def test_sweep_shapes_one_prepared_batch(pkg, oracle, ctx, dev, kernel):
+    """The same 90 cases at full size as ONE prepared grouped launch (the form the benchmark times):
+    automatic kernel choice, and the tiled kernel wherever it applies."""
+    import torch
+
+    cases = [(M, K, N, sp) for (M, K) in SWEEP_SHAPES for sp in SWEEP_SPARSITIES for N in SWEEP_WIDTHS]
+    arr = pkg.ProblemArray(len(cases))
+    keep, outs = [], []
+    for i, (M, K, N, sp) in enumerate(cases):
+        ro, ci, vals, B = sweep_case(pkg, M, K, N, sp)
+        d = (to_dev(vals, dev), to_dev(ro, dev), to_dev(ci, dev), to_dev(B, dev))
+        Cd = torch.full((M * N,), float("nan"), device=dev)
+        arr.set(i, M, K, N, int(ci.size), *d, Cd)
+        keep.append((ro, ci, vals, B, d))
+        outs.append(Cd)
+    ctx.set_option(pkg.OPT_SPMM_KERNEL, kernel)
+    try:
+        batch = ctx.batch_create(arr)
+        batch.launch()
+        torch.cuda.synchronize()
+        assert batch.info(check_device=True)[2] == 0, "a bounded wait ran out"
+        batch.close()
+    finally:
+        ctx.set_option(pkg.OPT_SPMM_KERNEL, 0)
+    for (M, K, N, sp), (ro, ci, vals, B, _d), Cd in zip(cases, keep, outs):
+        check(oracle, ro, ci, vals, B, M, N, Cd.cpu().numpy().reshape(M, N))
 
 
 @pytest.mark.parametrize("N", [4, 8, 12, 16, 20, 32, 36, 48, 64])
