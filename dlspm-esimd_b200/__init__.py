@@ -46,6 +46,26 @@ class Problem(C.Structure):
     ]
 
 
+class SddmmProblem(C.Structure):
+    """Mirror of `dlspm_sddmm_problem`."""
+
+    _fields_ = [
+        ("M", C.c_int), ("K", C.c_int), ("N", C.c_int), ("nnz", C.c_int),
+        ("row_offsets", C.c_void_p), ("column_indices", C.c_void_p), ("mask_values", C.c_void_p),
+        ("lhs", C.c_void_p), ("rhs", C.c_void_p), ("out_values", C.c_void_p),
+    ]
+
+
+class FusedProblem(C.Structure):
+    """Mirror of `dlspm_fused_problem`."""
+
+    _fields_ = [
+        ("M", C.c_int), ("K", C.c_int), ("N", C.c_int), ("nnz", C.c_int),
+        ("row_offsets", C.c_void_p), ("column_indices", C.c_void_p),
+        ("C", C.c_void_p), ("B", C.c_void_p), ("D", C.c_void_p), ("E", C.c_void_p),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 _P = C.c_void_p
@@ -67,6 +87,10 @@ _SIGNATURES = {
     "dlspm_plan_create": (_I, [_P, _I, _I, _I, _P, _P, _P, C.POINTER(_P)]),
     "dlspm_plan_destroy": (_I, [_P]),
     "dlspm_spmm_batched_f32": (_I, [_P, _I, C.POINTER(Problem), _P]),
+    "dlspm_sddmm_batched_f32": (_I, [_P, _I, C.POINTER(SddmmProblem), _P]),
+    "dlspm_fused_batched_f32": (_I, [_P, _I, C.POINTER(FusedProblem), _P]),
+    "dlspm_sddmm_batched_f32_host": (_I, [_P, _I, C.POINTER(SddmmProblem)]),
+    "dlspm_fused_batched_f32_host": (_I, [_P, _I, C.POINTER(FusedProblem)]),
     "dlspm_spmm_batched_f32_static": (_I, [_P, _I, C.POINTER(Problem), _P]),
     "dlspm_batch_create": (_I, [_P, _I, C.POINTER(Problem), C.POINTER(_P)]),
     "dlspm_batch_launch": (_I, [_P, _P, _P]),
@@ -108,6 +132,7 @@ _SIGNATURES = {
     "dlspm_mg_spmm_batched_f32_host": (_I, [_P, _I, C.POINTER(Problem)]),
     "dlspm_mg_spmm_rowshard_f32_host": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "dlspm_measure_fp32_peak": (_I, [_P, C.POINTER(C.c_double)]),
+    "dlspm_measure_fp32_peaks": (_I, [_P, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "dlspm_host_copy_count": (_I, [_P, C.POINTER(C.c_longlong)]),
     "dlspm_selftest_bounded_wait": (_I, [_P, C.c_uint, C.POINTER(_I)]),
     "dlspm_spmm_csr_f32_scatter": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _I, C.POINTER(_P), C.c_longlong, _P]),
@@ -321,6 +346,22 @@ class Context:
                                                       _stream_ptr(stream)),
                "dlspm_spmm_batched_f32_static", self)
 
+    def sddmm_batched(self, problems: "RowProblemArray", stream=None) -> None:
+        _check(self.lib.dlspm_sddmm_batched_f32(self.handle, len(problems), problems.array, _stream_ptr(stream)),
+               "dlspm_sddmm_batched_f32", self)
+
+    def fused_batched(self, problems: "RowProblemArray", stream=None) -> None:
+        _check(self.lib.dlspm_fused_batched_f32(self.handle, len(problems), problems.array, _stream_ptr(stream)),
+               "dlspm_fused_batched_f32", self)
+
+    def sddmm_batched_host(self, problems: "RowProblemArray") -> None:
+        _check(self.lib.dlspm_sddmm_batched_f32_host(self.handle, len(problems), problems.array),
+               "dlspm_sddmm_batched_f32_host", self)
+
+    def fused_batched_host(self, problems: "RowProblemArray") -> None:
+        _check(self.lib.dlspm_fused_batched_f32_host(self.handle, len(problems), problems.array),
+               "dlspm_fused_batched_f32_host", self)
+
     def batch_create(self, problems: "ProblemArray") -> "Batch":
         h = _P()
         _check(self.lib.dlspm_batch_create(self.handle, len(problems), problems.array, C.byref(h)),
@@ -350,6 +391,12 @@ class Context:
     def spmm_batched_host(self, problems: "ProblemArray") -> None:
         _check(self.lib.dlspm_spmm_batched_f32_host(self.handle, len(problems), problems.array),
                "dlspm_spmm_batched_f32_host", self)
+
+    def measure_fp32_peaks(self):
+        """(TFLOP/s with scalar FMAs, TFLOP/s with packed two-wide FMAs)."""
+        a, b = C.c_double(), C.c_double()
+        _check(self.lib.dlspm_measure_fp32_peaks(self.handle, C.byref(a), C.byref(b)), "dlspm_measure_fp32_peaks", self)
+        return a.value, b.value
 
     def host_copy_count(self) -> int:
         """cudaMemcpyAsync calls issued so far by spmm_batched_host on this context."""
@@ -496,6 +543,49 @@ class ProblemArray:
         p = self.array[i]
         p.M, p.K, p.N, p.nnz = M, K, N, nnz
         p.values, p.row_offsets, p.column_indices, p.B, p.C = values, row_offsets, column_indices, B, Cout
+
+
+class RowProblemArray:
+    """A host array of `dlspm_sddmm_problem` (kind "sddmm") or `dlspm_fused_problem` (kind "fused");
+    keeps the arrays it points to alive.  `host=True`: numpy / CPU tensors instead of CUDA tensors."""
+
+    def __init__(self, kind: str, n: int, host: bool = False):
+        assert kind in ("sddmm", "fused")
+        self.kind, self.n, self.host = kind, n, host
+        self.array = ((SddmmProblem if kind == "sddmm" else FusedProblem) * max(n, 1))()
+        self.keep = []
+
+    def __len__(self) -> int:
+        return self.n
+
+    def _ptr(self, a, dtype_np, what):
+        if self.host:
+            return _host_ptr(a, dtype_np, what)
+        import torch
+
+        return _dev_ptr(a, torch.int32 if dtype_np == np.int32 else torch.float32, what)
+
+    def set_sddmm(self, i, M, K, N, nnz, row_offsets, column_indices, lhs, rhs, out_values, mask_values=None) -> None:
+        p = self.array[i]
+        p.M, p.K, p.N, p.nnz = M, K, N, nnz
+        p.row_offsets = self._ptr(row_offsets, np.int32, "row_offsets")
+        p.column_indices = self._ptr(column_indices, np.int32, "column_indices")
+        p.mask_values = self._ptr(mask_values, np.float32, "mask_values")
+        p.lhs = self._ptr(lhs, np.float32, "lhs")
+        p.rhs = self._ptr(rhs, np.float32, "rhs")
+        p.out_values = self._ptr(out_values, np.float32, "out_values")
+        self.keep.append((row_offsets, column_indices, mask_values, lhs, rhs, out_values))
+
+    def set_fused(self, i, M, K, N, nnz, row_offsets, column_indices, Cq, Bk, Dv, Eo) -> None:
+        p = self.array[i]
+        p.M, p.K, p.N, p.nnz = M, K, N, nnz
+        p.row_offsets = self._ptr(row_offsets, np.int32, "row_offsets")
+        p.column_indices = self._ptr(column_indices, np.int32, "column_indices")
+        p.C = self._ptr(Cq, np.float32, "C")
+        p.B = self._ptr(Bk, np.float32, "B")
+        p.D = self._ptr(Dv, np.float32, "D")
+        p.E = self._ptr(Eo, np.float32, "E")
+        self.keep.append((row_offsets, column_indices, Cq, Bk, Dv, Eo))
 
 
 class Batch:

@@ -72,6 +72,13 @@ size_t dlspm_batched_table_bytes(int count);
 int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *problems, void *tables, cudaStream_t st,
                           void *pinned = nullptr);
 
+// Grouped SDDMM / fused launches with caller-provided table memory (sddmm_batch.cu).
+size_t dlspm_rows_batched_table_bytes(int count);
+int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems, void *tables, void *pinned,
+                           cudaStream_t st);
+int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems, void *tables, void *pinned,
+                           cudaStream_t st);
+
 static inline int dlspm_ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long dlspm_ceil_div64(long long a, long long b) { return (a + b - 1) / b; }
 

@@ -182,6 +182,50 @@ __global__ void __launch_bounds__(256) fma_peak_kernel(float *sink, int iters, f
     if (s == -12345.678f) sink[0] = s;
 }
 
+// The same with packed multiply-adds (fma.rn.f32x2): two per instruction.
+__global__ void __launch_bounds__(256) fma2_peak_kernel(float *sink, int iters, float seed)
+{
+    float2 a0 = make_float2(seed + threadIdx.x, seed), a1 = make_float2(a0.x + 1.f, 1.f), a2 = make_float2(a0.x + 2.f, 2.f),
+           a3 = make_float2(a0.x + 3.f, 3.f);
+    const float2 m = make_float2(0.999f, 0.998f), c = make_float2(0.001f, 0.002f);
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            a0 = __ffma2_rn(a0, m, c); a1 = __ffma2_rn(a1, m, c); a2 = __ffma2_rn(a2, m, c); a3 = __ffma2_rn(a3, m, c);
+        }
+    }
+    const float s = a0.x + a0.y + a1.x + a1.y + a2.x + a2.y + a3.x + a3.y;
+    if (s == -12345.678f) sink[0] = s;
+}
+
+extern "C" int dlspm_measure_fp32_peaks(dlspm_ctx *ctx, double *scalar_tflops, double *packed_tflops)
+{
+    if (!ctx || !scalar_tflops || !packed_tflops) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_measure_fp32_peak(ctx, scalar_tflops);
+    if (rc) return rc;
+    const int iters = 4096;
+    const int blocks = ctx->sm_count * 8;
+    cudaEvent_t e0, e1;
+    DLSPM_CUDA_TRY(ctx, cudaEventCreate(&e0));
+    DLSPM_CUDA_TRY(ctx, cudaEventCreate(&e1));
+    float best_ms = 1e30f;
+    for (int rep = 0; rep < 5; rep++) {
+        cudaEventRecord(e0, ctx->stream);
+        fma2_peak_kernel<<<blocks, 256, 0, ctx->stream>>>((float *)ctx->scratch, iters, 1.0f);
+        cudaEventRecord(e1, ctx->stream);
+        DLSPM_CUDA_TRY(ctx, cudaEventSynchronize(e1));
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best_ms) best_ms = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    // 4 chains x 2 lanes x 8 unrolled = 64 multiply-adds per thread and iteration, as in the scalar probe
+    *packed_tflops = 2.0 * 64.0 * (double)iters * 256.0 * (double)blocks / (best_ms * 1e-3) * 1e-12;
+    return DLSPM_OK;
+}
+
 extern "C" int dlspm_measure_fp32_peak(dlspm_ctx *ctx, double *tflops)
 {
     if (!ctx || !tflops) return DLSPM_ERR_INVALID_ARGUMENT;

@@ -378,6 +378,153 @@ static int dlspm_spmm_batched_f32_host_impl(dlspm_ctx *ctx, int count, const dls
     return DLSPM_OK;
 }
 
+// ---- grouped SDDMM and fused chain with host pointers ---------------------------------------------
+// Pieces of up to 256 MiB of device copies, one after the other on the context's stream: inputs in
+// (merged into few copies where the caller's arrays are neighbours in one pinned allocation), one
+// grouped launch, results out.
+namespace {
+
+struct SddmmTraits {
+    typedef dlspm_sddmm_problem Problem;
+    static bool valid(const Problem &q)
+    {
+        return q.M >= 0 && q.K >= 0 && q.N >= 0 && q.nnz >= 0 && q.row_offsets &&
+               (q.nnz == 0 || (q.column_indices && q.out_values)) && ((size_t)q.M * q.N == 0 || q.lhs) &&
+               ((size_t)q.K * q.N == 0 || q.rhs);
+    }
+    static size_t need(const Problem &q)
+    {
+        return padded(4 * ((size_t)q.M + 1)) + 3 * padded(4 * (size_t)q.nnz) + padded(4 * (size_t)q.M * q.N) +
+               padded(4 * (size_t)q.K * q.N);
+    }
+    // carves the device arrays of one problem, queues its input copies, returns the device problem
+    static int stage(RunCopier &in, Carver &cv, const Problem &q, Problem &d)
+    {
+        d = q;
+        int *ro = cv.take<int>((size_t)q.M + 1);
+        int *ci = cv.take<int>((size_t)q.nnz);
+        float *mask = q.mask_values ? cv.take<float>((size_t)q.nnz) : nullptr;
+        float *lhs = cv.take<float>((size_t)q.M * q.N);
+        float *rhs = cv.take<float>((size_t)q.K * q.N);
+        int rc = in.add(ro, q.row_offsets, 4 * ((size_t)q.M + 1));
+        if (!rc) rc = in.add(ci, q.column_indices, 4 * (size_t)q.nnz);
+        if (!rc && mask) rc = in.add(mask, q.mask_values, 4 * (size_t)q.nnz);
+        if (!rc) rc = in.add(lhs, q.lhs, 4 * (size_t)q.M * q.N);
+        if (!rc) rc = in.add(rhs, q.rhs, 4 * (size_t)q.K * q.N);
+        d.row_offsets = ro;
+        d.column_indices = ci;
+        d.mask_values = mask;
+        d.lhs = lhs;
+        d.rhs = rhs;
+        return rc;
+    }
+    static void carve_out(Carver &cv, const Problem &q, Problem &d) { d.out_values = cv.take<float>((size_t)q.nnz); }
+    static int unstage(RunCopier &out, const Problem &q, const Problem &d) { return out.add(d.out_values, q.out_values, 4 * (size_t)q.nnz); }
+    static int run(dlspm_ctx *ctx, int n, const Problem *d, void *tables, cudaStream_t st) { return dlspm_sddmm_batched_at(ctx, n, d, tables, nullptr, st); }
+};
+
+struct FusedTraits {
+    typedef dlspm_fused_problem Problem;
+    static bool valid(const Problem &q)
+    {
+        return q.M >= 0 && q.K >= 0 && q.N >= 0 && q.nnz >= 0 && q.row_offsets && (q.nnz == 0 || q.column_indices) &&
+               ((size_t)q.M * q.N == 0 || (q.C && q.E)) && ((size_t)q.K * q.N == 0 || (q.B && q.D));
+    }
+    static size_t need(const Problem &q)
+    {
+        return padded(4 * ((size_t)q.M + 1)) + padded(4 * (size_t)q.nnz) + 2 * padded(4 * (size_t)q.M * q.N) +
+               2 * padded(4 * (size_t)q.K * q.N);
+    }
+    static int stage(RunCopier &in, Carver &cv, const Problem &q, Problem &d)
+    {
+        d = q;
+        int *ro = cv.take<int>((size_t)q.M + 1);
+        int *ci = cv.take<int>((size_t)q.nnz);
+        float *c = cv.take<float>((size_t)q.M * q.N);
+        float *b = cv.take<float>((size_t)q.K * q.N);
+        float *dd = cv.take<float>((size_t)q.K * q.N);
+        int rc = in.add(ro, q.row_offsets, 4 * ((size_t)q.M + 1));
+        if (!rc) rc = in.add(ci, q.column_indices, 4 * (size_t)q.nnz);
+        if (!rc) rc = in.add(c, q.C, 4 * (size_t)q.M * q.N);
+        if (!rc) rc = in.add(b, q.B, 4 * (size_t)q.K * q.N);
+        if (!rc) rc = in.add(dd, q.D, 4 * (size_t)q.K * q.N);
+        d.row_offsets = ro;
+        d.column_indices = ci;
+        d.C = c;
+        d.B = b;
+        d.D = dd;
+        return rc;
+    }
+    static void carve_out(Carver &cv, const Problem &q, Problem &d) { d.E = cv.take<float>((size_t)q.M * q.N); }
+    static int unstage(RunCopier &out, const Problem &q, const Problem &d) { return out.add(d.E, q.E, 4 * (size_t)q.M * q.N); }
+    static int run(dlspm_ctx *ctx, int n, const Problem *d, void *tables, cudaStream_t st) { return dlspm_fused_batched_at(ctx, n, d, tables, nullptr, st); }
+};
+
+template <typename T>
+int rows_batched_host(dlspm_ctx *ctx, int count, const typename T::Problem *problems)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    for (int i = 0; i < count; i++)
+        if (!T::valid(problems[i])) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (count == 0) return DLSPM_OK;
+    const size_t budget = (size_t)256 << 20;
+    std::vector<int> piece_end;
+    size_t max_piece = 0, max_tables = 0;
+    for (int first = 0; first < count;) {
+        size_t bytes = 0;
+        int last = first;
+        while (last < count && (last == first || bytes + T::need(problems[last]) <= budget)) bytes += T::need(problems[last++]);
+        piece_end.push_back(last);
+        max_piece = std::max(max_piece, bytes);
+        max_tables = std::max(max_tables, dlspm_rows_batched_table_bytes(last - first));
+        first = last;
+    }
+    rc = dlspm_stage_reserve(ctx, padded(max_tables) + padded(max_piece) + 256);
+    if (rc) return rc;
+    cudaStream_t st = ctx->stream;
+    std::vector<typename T::Problem> dev;
+    int first = 0;
+    for (int last : piece_end) {
+        Carver cv((char *)ctx->stage + padded(max_tables));
+        dev.assign((size_t)(last - first), typename T::Problem());
+        RunCopier in(ctx, st, true);
+        for (int i = first; i < last; i++) {
+            rc = T::stage(in, cv, problems[i], dev[(size_t)(i - first)]);
+            if (rc) return rc;
+        }
+        rc = in.flush();
+        if (rc) return rc;
+        for (int i = first; i < last; i++) T::carve_out(cv, problems[i], dev[(size_t)(i - first)]);
+        rc = T::run(ctx, last - first, dev.data(), ctx->stage, st);
+        if (rc) return rc;
+        RunCopier out(ctx, st, false);
+        for (int i = first; i < last; i++) {
+            rc = T::unstage(out, problems[i], dev[(size_t)(i - first)]);
+            if (rc) return rc;
+        }
+        rc = out.flush();
+        if (rc) return rc;
+        // the staging memory is reused by the next piece
+        DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(st));
+        first = last;
+    }
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+extern "C" int dlspm_sddmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems)
+{
+    return drain_on_error(ctx, rows_batched_host<SddmmTraits>(ctx, count, problems));
+}
+
+extern "C" int dlspm_fused_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems)
+{
+    return drain_on_error(ctx, rows_batched_host<FusedTraits>(ctx, count, problems));
+}
+
 // ---- exported entry points: the implementations above plus the drain on failure ---------------------
 extern "C" int dlspm_spmm_csr_f32_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const float *values,
                                        const int *row_offsets, const int *column_indices, const float *B,

@@ -1,0 +1,324 @@
+// Grouped launches over many independent SDDMMs and fused SDDMM -> SpMM chains for sm_100a.
+//
+// A layer-sized pattern (a few hundred to a few thousand rows) is launch-bound on its own: the lone
+// launches of the reference's batch scripts (SDDMM/batch-run-sddmm_fromfile:31-47,
+// FUSED/batch-run-fused:22-34) spend more time between kernels than in them.  Here all problems of a
+// batch that share a register layout (group width G and chunks per lane R, which follow from the
+// inner dimension, see sddmm_device.cuh) run in ONE persistent launch: thread blocks pull tiles of
+// eight rows from a device counter, one warp per row, and every row is processed exactly as in the
+// single-matrix kernels (same passes, same butterfly, same order of additions), so results have the
+// same bits.  A batch with one inner dimension is one launch; a mixed batch is at most six.
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+#include "fused_device.cuh"
+#include "sddmm_device.cuh"
+
+using namespace dlspm;
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kClasses = 6;  // (G, R) layouts of sddmm_layout
+constexpr int kOpSddmm = 0, kOpFused = 1;
+
+struct RowProblem {
+    const int *row_offsets;
+    const int *cols;
+    const float *a;     // lhs (SDDMM) or C (fused): M x N
+    const float *b;     // rhs or B: K x N
+    const float *d;     // fused only: D, K x N
+    const float *mask;  // SDDMM only: factors per stored entry or nullptr
+    float *out;         // out_values (SDDMM) or E (fused)
+    int M;
+    int chunks;         // N / 4
+};
+
+template <int G, int R>
+__device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int lane)
+{
+    const int g = lane / G, t = lane % G;
+    const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+    if (start >= end) return;
+    const float4 *lhs4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
+    const float4 *rhs4 = reinterpret_cast<const float4 *>(p.b);
+    float4 a[R];
+    load_row_chunks<G, R>(lhs4, p.chunks, t, a);
+    int col_next = start + lane < end ? __ldg(p.cols + start + lane) : -1;
+    for (int base = start; base < end; base += 32) {
+        const int q = base + lane;
+        const int col = col_next;
+        col_next = q + 32 < end ? __ldg(p.cols + q + 32) : -1;
+        const float r = sddmm_pass<G, R>(a, rhs4, p.chunks, col, g, t);
+        if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * r : r;
+    }
+}
+
+template <int G, int R>
+__device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int lane)
+{
+    const int g = lane / G, t = lane % G;
+    const float4 *c4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
+    float4 q[R];
+    load_row_chunks<G, R>(c4, p.chunks, t, q);
+    float4 acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float run_max = -INFINITY, run_sum = 0.f;
+    fused_row_passes<G, R, kPlain>(p.cols, q, reinterpret_cast<const float4 *>(p.b),
+                                   reinterpret_cast<const float4 *>(p.d), p.chunks, __ldg(p.row_offsets + row),
+                                   __ldg(p.row_offsets + row + 1), 32, 1.f, lane, acc, run_max, run_sum);
+    if (g == 0) {  // rows without entries are written as zeros
+        float4 *e4 = reinterpret_cast<float4 *>(p.out) + (size_t)row * (size_t)p.chunks;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int idx = r * G + t;
+            if (idx < p.chunks) e4[idx] = acc[r];
+        }
+    }
+}
+
+// Persistent thread blocks pull tile numbers (eight rows of one problem) from a device counter;
+// tile_start[i] is the first tile of problem i, tile_start[count] the total.
+template <int G, int R, int OP>
+__global__ void __launch_bounds__(kWarps * 32)
+rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__restrict__ tile_start, int count,
+                    unsigned long long *counter)
+{
+    __shared__ unsigned long long s_tile;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long total = tile_start[count];
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(counter, 1ull);
+        __syncthreads();
+        const long long tile = (long long)s_tile;
+        __syncthreads();
+        if (tile >= total) break;
+        int lo = 0, hi = count - 1;  // last problem whose first tile is <= tile
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(tile_start + mid) <= tile) lo = mid;
+            else hi = mid - 1;
+        }
+        const RowProblem p = problems[lo];
+        const int row = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
+        if (row < p.M) {
+            if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, lane);
+            else fused_one_row<G, R>(p, row, lane);
+        }
+    }
+}
+
+int layout_class(int G, int R)
+{
+    if (G == 8) return R == 1 ? 0 : R == 2 ? 1 : 2;
+    if (G == 16) return 3;
+    return R == 4 ? 4 : 5;
+}
+
+template <int G, int R, int OP>
+int launch_class(dlspm_ctx *ctx, const RowProblem *d_tab, const long long *d_starts, int count, long long tiles,
+                 unsigned long long *d_counter, cudaStream_t st)
+{
+    int per_sm = 0;
+    DLSPM_CUDA_TRY(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rows_batched_kernel<G, R, OP>, kWarps * 32, 0));
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * std::max(per_sm, 1));
+    rows_batched_kernel<G, R, OP><<<(unsigned)want, kWarps * 32, 0, st>>>(d_tab, d_starts, count, d_counter);
+    DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+    return DLSPM_OK;
+}
+
+template <int OP>
+int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, const long long *d_starts, int count,
+                          long long tiles, unsigned long long *d_counter, cudaStream_t st)
+{
+    switch (cls) {
+    case 0: return launch_class<8, 1, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 1: return launch_class<8, 2, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 2: return launch_class<8, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 3: return launch_class<16, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 4: return launch_class<32, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    default: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    }
+}
+
+struct HostEntry {
+    RowProblem p;
+    double work;
+    int index;
+};
+
+// Device layout of the tables of one call inside `tables`: per class its problems, then its tile
+// index, then all counters.
+size_t padded256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+}  // namespace
+
+// Bytes of device memory the tables of a grouped SDDMM / fused launch of `count` problems need.
+size_t dlspm_rows_batched_table_bytes(int count)
+{
+    return padded256(sizeof(RowProblem) * (size_t)count) + (size_t)kClasses * 256 +
+           padded256(sizeof(long long) * ((size_t)count + kClasses)) + 256 * (size_t)kClasses + 256;
+}
+
+namespace {
+
+// Launches the grouped kernels for the entries (already validated, all eligible for the 128-bit
+// path) with their tables at `tables`; `pinned` (optional) is host memory of the same size to build
+// the tables in, for asynchronous copies.
+template <int OP>
+int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses], void *tables, void *pinned,
+                    cudaStream_t st)
+{
+    size_t total = 0;
+    for (int c = 0; c < kClasses; c++) total += by_class[c].size();
+    if (total == 0) return DLSPM_OK;
+    // host image of the tables
+    const size_t tab_bytes = padded256(sizeof(RowProblem) * total) + (size_t)kClasses * 256;
+    const size_t starts_bytes = padded256(sizeof(long long) * (total + kClasses)) + 256 * (size_t)kClasses;
+    const size_t image_bytes = tab_bytes + starts_bytes;
+    std::vector<unsigned char> local;
+    unsigned char *img = (unsigned char *)pinned;
+    if (!img) {
+        local.resize(image_bytes);
+        img = local.data();
+    }
+    size_t tab_off[kClasses], st_off[kClasses];
+    long long tiles[kClasses];
+    size_t toff = 0, soff = tab_bytes;
+    for (int c = 0; c < kClasses; c++) {
+        std::vector<HostEntry> &v = by_class[c];
+        std::stable_sort(v.begin(), v.end(), [](const HostEntry &x, const HostEntry &y) { return x.work > y.work; });
+        tab_off[c] = toff;
+        st_off[c] = soff;
+        RowProblem *tab = (RowProblem *)(img + toff);
+        long long *starts = (long long *)(img + soff);
+        long long run = 0;
+        for (size_t i = 0; i < v.size(); i++) {
+            tab[i] = v[i].p;
+            starts[i] = run;
+            run += dlspm_ceil_div(v[i].p.M, kWarps);
+        }
+        starts[v.size()] = run;
+        tiles[c] = run;
+        toff += padded256(sizeof(RowProblem) * v.size());
+        soff += padded256(sizeof(long long) * (v.size() + 1));
+    }
+    char *base = (char *)tables;
+    unsigned long long *d_counters = (unsigned long long *)(base + image_bytes);
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, img, image_bytes, cudaMemcpyHostToDevice, st));
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counters, 0, 256, st));
+    for (int c = 0; c < kClasses; c++) {
+        if (by_class[c].empty() || tiles[c] == 0) continue;
+        int rc = launch_class_by_index<OP>(ctx, c, (const RowProblem *)(base + tab_off[c]),
+                                           (const long long *)(base + st_off[c]), (int)by_class[c].size(), tiles[c],
+                                           d_counters + c, st);
+        if (rc) return rc;
+    }
+    return DLSPM_OK;
+}
+
+int reject_capture(dlspm_ctx *ctx, cudaStream_t st, const char *who)
+{
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &status) != cudaSuccess) {
+        (void)cudaGetLastError();
+        status = cudaStreamCaptureStatusActive;
+    }
+    if (status != cudaStreamCaptureStatusNone) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "%s: the stream is being captured; grouped launches copy tables from host memory and cannot be recorded",
+                 who);
+        return DLSPM_ERR_UNSUPPORTED;
+    }
+    return DLSPM_OK;
+}
+
+}  // namespace
+
+// SDDMM: classifies the problems; eligible ones go to the grouped kernels (tables at `tables`), the
+// others run one by one through the single-matrix entry point on the same stream.
+int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems, void *tables, void *pinned,
+                           cudaStream_t st)
+{
+    std::vector<HostEntry> by_class[kClasses];
+    for (int i = 0; i < count; i++) {
+        const dlspm_sddmm_problem &q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.N < 0 || q.nnz < 0 || (q.M > 0 && !q.row_offsets) ||
+            (q.nnz > 0 && (!q.column_indices || !q.out_values)) || (q.nnz > 0 && q.N > 0 && (!q.lhs || !q.rhs)))
+            return DLSPM_ERR_INVALID_ARGUMENT;
+    }
+    for (int i = 0; i < count; i++) {
+        const dlspm_sddmm_problem &q = problems[i];
+        if (q.M == 0 || q.nnz == 0) continue;
+        int G = 0, R = 0;
+        if (q.N > 0 && dlspm_vec_width(q.N, q.lhs, q.rhs) == 4 && sddmm_layout(q.N / 4, &G, &R)) {
+            HostEntry e;
+            e.p = RowProblem{q.row_offsets, q.column_indices, q.lhs, q.rhs, nullptr, q.mask_values, q.out_values, q.M, q.N / 4};
+            e.work = (double)q.nnz * q.N;
+            e.index = i;
+            by_class[layout_class(G, R)].push_back(e);
+        } else {
+            int rc = dlspm_sddmm_csr_masked_f32(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices, q.mask_values,
+                                                q.lhs, q.rhs, q.out_values, st);
+            if (rc) return rc;
+        }
+    }
+    return rows_batched_at<kOpSddmm>(ctx, by_class, tables, pinned, st);
+}
+
+int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems, void *tables, void *pinned,
+                           cudaStream_t st)
+{
+    std::vector<HostEntry> by_class[kClasses];
+    for (int i = 0; i < count; i++) {
+        const dlspm_fused_problem &q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.N < 0 || q.nnz < 0 || (q.M > 0 && !q.row_offsets) || (q.nnz > 0 && !q.column_indices) ||
+            (q.M > 0 && q.N > 0 && (!q.C || !q.E)) || (q.nnz > 0 && q.N > 0 && (!q.B || !q.D)))
+            return DLSPM_ERR_INVALID_ARGUMENT;
+    }
+    for (int i = 0; i < count; i++) {
+        const dlspm_fused_problem &q = problems[i];
+        if (q.M == 0 || q.N == 0) continue;
+        int G = 0, R = 0;
+        if (dlspm_vec_width(q.N, q.C, q.B, q.D, q.E) == 4 && sddmm_layout(q.N / 4, &G, &R)) {
+            HostEntry e;
+            e.p = RowProblem{q.row_offsets, q.column_indices, q.C, q.B, q.D, nullptr, q.E, q.M, q.N / 4};
+            e.work = (double)q.nnz * q.N + (double)q.M;  // rows without entries still cost a store
+            e.index = i;
+            by_class[layout_class(G, R)].push_back(e);
+        } else {
+            int rc = dlspm_fused_sddmm_spmm_f32(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices, q.C, q.B, q.D,
+                                                q.E, st);
+            if (rc) return rc;
+        }
+    }
+    return rows_batched_at<kOpFused>(ctx, by_class, tables, pinned, st);
+}
+
+extern "C" int dlspm_sddmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems, void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (count == 0) return DLSPM_OK;
+    rc = reject_capture(ctx, (cudaStream_t)stream, "dlspm_sddmm_batched_f32");
+    if (rc) return rc;
+    rc = dlspm_scratch_reserve(ctx, dlspm_rows_batched_table_bytes(count));
+    if (rc) return rc;
+    return dlspm_sddmm_batched_at(ctx, count, problems, ctx->scratch, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int dlspm_fused_batched_f32(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems, void *stream)
+{
+    if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (count == 0) return DLSPM_OK;
+    rc = reject_capture(ctx, (cudaStream_t)stream, "dlspm_fused_batched_f32");
+    if (rc) return rc;
+    rc = dlspm_scratch_reserve(ctx, dlspm_rows_batched_table_bytes(count));
+    if (rc) return rc;
+    return dlspm_fused_batched_at(ctx, count, problems, ctx->scratch, nullptr, (cudaStream_t)stream);
+}

@@ -257,31 +257,25 @@ int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long lo
     return DLSPM_OK;
 }
 
-int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long *d_starts,
-                       unsigned long long *d_counter, int *d_error, int count, long long tiles, cudaStream_t st)
+int tile_launch_tables(dlspm_ctx *ctx, const TileProblem *d_tab, const long long *d_starts, int *d_error, int count,
+                       long long tiles, cudaStream_t st)
 {
     if (count == 0 || tiles == 0) return DLSPM_OK;
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];
     const size_t smem = sizeof(TileSmem);
-    if (ctx->device < 64 && !attr_set[ctx->device]) {
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[ctx->device] = true;
+    if (ctx->device >= 64 || !attr_set[ctx->device].load(std::memory_order_acquire)) {
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DLSPM_CUDA_TRY(ctx, cudaFuncSetAttribute(spmm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (ctx->device < 64) attr_set[ctx->device].store(true, std::memory_order_release);
     }
-    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
-    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 2);
+    // one block per SM (its shared memory fills the SM); blocks deal the tiles out among themselves
+    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count);
     dim3 grid((unsigned)want), block(kTileThreads);
-    // kernel choice 3: absent entries are multiplied as zeros (no mask tests in the inner loop)
-    const bool dense = ctx->spmm_kernel == 3;
-    if (dense) {
-        if (ctx->strict_fp32) spmm_tile_kernel<true, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
-        else spmm_tile_kernel<false, true><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
-    } else {
-        if (ctx->strict_fp32) spmm_tile_kernel<true, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
-        else spmm_tile_kernel<false, false><<<grid, block, smem, st>>>(d_tab, d_starts, count, d_counter, d_error);
-    }
+    // kernel choice 2: present entries only, under a mask, in every chunk; otherwise absent entries
+    // are multiplied as zeros except in chunks of B that hold a non-finite value
+    const int force_masked = ctx->spmm_kernel == 2 ? 1 : 0;
+    if (ctx->strict_fp32) spmm_tile_kernel<true><<<grid, block, smem, st>>>(d_tab, d_starts, count, force_masked, d_error);
+    else spmm_tile_kernel<false><<<grid, block, smem, st>>>(d_tab, d_starts, count, force_masked, d_error);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
@@ -373,8 +367,6 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
             tp.row_blocks = dlspm_ceil_div(t.M, kTileM);
             tp.col_blocks = dlspm_ceil_div(t.N, kTileN);
             tp.pad = 0;
-            tstarts.push_back(trun);
-            trun += (long long)tp.row_blocks * tp.col_blocks;
             ttab.push_back(tp);
         } else {
             gstarts.push_back(grun);
@@ -383,6 +375,14 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
         }
     }
     gstarts.push_back(grun);
+    // A tile of the tiled kernel costs ceil(K / 32) equal steps: with the problems in order of
+    // decreasing K the fixed deal of tiles to thread blocks (block b takes tiles b, b + blocks, ...)
+    // hands every block the same mix, the longest tiles first.
+    std::stable_sort(ttab.begin(), ttab.end(), [](const TileProblem &x, const TileProblem &y) { return x.K > y.K; });
+    for (const TileProblem &tp : ttab) {
+        tstarts.push_back(trun);
+        trun += (long long)tp.row_blocks * tp.col_blocks;
+    }
     tstarts.push_back(trun);
     b->count = (int)gtab.size();
     b->tiles = grun;
@@ -414,8 +414,7 @@ extern "C" int dlspm_batch_launch_part(dlspm_ctx *ctx, const dlspm_batch *batch,
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (part != 1) {
-        rc = tile_launch_tables(ctx, batch->tproblems, batch->ttile_start, batch->counters + 1, batch->error,
-                                batch->tcount, batch->ttiles, st);
+        rc = tile_launch_tables(ctx, batch->tproblems, batch->ttile_start, batch->error, batch->tcount, batch->ttiles, st);
         if (rc) return rc;
     }
     if (part != 2) {

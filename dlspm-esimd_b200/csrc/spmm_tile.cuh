@@ -1,33 +1,48 @@
-// Tiled SpMM for the denser problems (from roughly 15-20 % nonzeros, rows with strictly ascending
-// columns): a thread block owns 64 rows x 256 columns of C and walks K in chunks of 32 rows of B.
+// Tiled SpMM for the denser problems (from roughly a quarter nonzeros, rows with strictly ascending
+// columns): one thread block per SM owns 128 rows x 256 columns of C at a time and walks K in chunks
+// of 32 rows of B.
 //
 // The row-gather kernel moves 512 bytes of B through L1 for every nonzero and 128 columns; ncu shows
-// it at 87 % of the L1 data-pipe peak, i.e. at its ceiling (about one fifth of the fp32 peak).  The
-// way past that ceiling is to load a row of B once and use it for several rows of A.  Here a warp
-// owns 8 rows of the tile and all 256 columns (8 per lane):
-//   * the B chunk (32 rows x 1 KiB) comes into shared memory by bulk asynchronous copies
-//     (cp.async.bulk, one per row, completion counted on an mbarrier), double buffered;
-//   * each warp turns the next 32 columns of its 8 rows from CSR into a small dense block plus one
-//     32-bit presence mask per row: the <= 32 next entries of a row are fetched with cp.async
-//     straight into shared memory while the previous chunk is being computed, then the entries that
-//     fall into the chunk (a prefix, since columns ascend) are scattered by column;
-//   * per column k of the chunk the warp loads its 8 columns of B[k] once (two 128-bit loads) and
-//     walks its 8 rows: the mask bit guards the 8 FMAs of an entry (the compiler predicates them;
-//     explicit branches measured slower).  Columns that no row of the warp uses are skipped before
-//     the B load.
-// Only present entries are multiplied, in ascending column order, so every output element sums the
-// same products in the same order as the row-gather kernel and the reference host loop
-// (SPMM/spmm-esimd-fromfile.cpp:63-83): results are bit-identical to the row-gather kernel.
+// it at 87 % of the L1 data-pipe peak, i.e. at its ceiling (one L1 wavefront per FMA instruction, a
+// quarter of the fp32 peak).  The way past that ceiling is to load a row of B once and use it for
+// several rows of A from registers.  Roles inside a block of 17 warps, which never meet at a
+// block-wide barrier:
+//   * one producer warp streams B: the 32 x 256 chunk of every (tile, chunk) step goes into one of
+//     four shared-memory stages by bulk asynchronous copies (cp.async.bulk, one per row, completion
+//     counted on the stage's `full` mbarrier).  When a chunk has landed the producer tests it for
+//     non-finite values (one pass over 32 KiB against the chunk's 524 k multiply-adds), records the
+//     answer and arrives on the stage's `ready` mbarrier.  A stage is refilled once all sixteen
+//     consumer warps have arrived on its `empty` mbarrier.
+//   * sixteen consumer warps own 8 rows of the tile each and all 256 columns (8 per lane, 64
+//     accumulators per lane).  Each warp turns the next 32 columns of its 8 rows from CSR into a
+//     zero-filled 32 x 8 block in shared memory (private to the warp, double buffered; the next <= 32
+//     entries of every row are fetched one chunk ahead with cp.async) plus one presence mask per
+//     row.  Per column k of the chunk the warp reads its 8 values of A (two broadcast loads) and its
+//     8 columns of B[k] (two 128-bit loads) and issues 64 FMAs.
+// Absent entries are multiplied as zeros, which adds +0 to a sum and leaves it unchanged as long as
+// B[k] is finite.  For a chunk in which the producer found an infinity or a NaN the consumers run
+// the masked loop instead, which multiplies present entries only, so a non-finite value of B
+// reaches exactly the rows that reference it, as in the reference host loop
+// (SPMM/spmm-esimd-fromfile.cpp:63-83).  Products are added in ascending column order from 0.0f:
+// results are bit-identical to the row-gather kernel (the one exception is the sign of a zero: a
+// sum that underflowed to -0 becomes +0 when a zero product is added to it).
+// Every mbarrier wait is bounded; a wait that runs out raises the block's abort word, which ends
+// all roles, sets the error word of the launch and leaves the tile unwritten.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace dlspm {
 
-constexpr int kTileM = 64, kTileN = 256, kTileK = 32;
-constexpr int kTileThreads = 256;
-constexpr int kTileRowsPerWarp = kTileM / 8;
-constexpr unsigned kWaitLimit = 1u << 24;  // polls of an mbarrier before the kernel gives up
+constexpr int kTileN = 256, kTileK = 32;
+constexpr int kTileConsumers = 16;               // consumer warps per block
+constexpr int kTileRowsPerWarp = 8;
+constexpr int kTileM = kTileConsumers * kTileRowsPerWarp;  // 128 rows of C per tile
+constexpr int kTileStages = 4;                   // B chunks in flight
+// Registers are handed out to a block in units of four warps, so the producer warp costs a whole
+// group of four: the block is launched with 20 warps, of which three leave at once.
+constexpr int kTileThreads = (kTileConsumers + 4) * 32;
+constexpr unsigned kWaitLimit = 1u << 20;  // polls of an mbarrier (a quarter of a microsecond apart) before the kernel gives up
 
 struct TileProblem {
     const float *values;
@@ -37,23 +52,22 @@ struct TileProblem {
     float *C;
     const int *row_order;  // rows from the longest to the shortest (nullptr: natural order)
     int M, K, N;
-    int row_blocks;  // ceil(M / 64)
+    int row_blocks;  // ceil(M / 128)
     int col_blocks;  // ceil(N / 256)
     int pad;
 };
 
 struct TileSmem {
-    float Bs[2][kTileK][kTileN];          // 64 KiB: B chunk, two stages
-    float As[2][kTileM][kTileK];          // 16 KiB: A chunk by (row, column in chunk); only masked entries are valid
-    int cand_col[kTileM][32];             //  8 KiB: next <= 32 entries of every row (staged by cp.async)
-    float cand_val[kTileM][32];           //  8 KiB
-    unsigned Am[2][kTileM];               // presence mask of the chunk per row
-    int cursor[kTileM];                   // next unconsumed entry of every row
-    int row_end[kTileM];
-    int row_id[kTileM];                   // row of C behind every tile slot (-1: none)
-    unsigned long long full[2];           // mbarriers: B chunk landed
-    unsigned long long tile;
-    int abort;                            // set by a thread whose bounded wait ran out
+    float Bs[kTileStages][kTileK][kTileN];                 // 128 KiB: B chunks
+    float As[kTileConsumers][2][kTileK][kTileRowsPerWarp]; //  32 KiB: per warp, A chunk by (column in chunk, row), zero-filled
+    int cand_col[kTileConsumers][kTileRowsPerWarp][32];    //  16 KiB: next <= 32 entries of every row (staged by cp.async)
+    float cand_val[kTileConsumers][kTileRowsPerWarp][32];  //  16 KiB
+    unsigned Am[kTileConsumers][2][kTileRowsPerWarp];      // presence mask of the chunk per row
+    unsigned long long full[kTileStages];                  // B chunk landed (transaction bytes)
+    unsigned long long ready[kTileStages];                 // B chunk landed and tested (producer arrives)
+    unsigned long long empty[kTileStages];                 // all consumer warps are done with the chunk
+    int nonfinite[kTileStages];                            // the chunk holds an infinity or a NaN
+    int abort;                                             // set by a thread whose bounded wait ran out
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,10 +112,59 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Issues the B chunk starting at row k0 into stage s (called by warp 0 only).  Rows past the end of
-// B (last chunk when K is not a multiple of 32) are written as zeros: the masked inner loop never
-// reads them, but the zero-filled variant multiplies every row of the chunk, and stale shared
-// memory there could hold a NaN.
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait that also gives up when another thread of the block has raised `abort`.
+__device__ __forceinline__ bool mbar_wait_or_abort(unsigned long long *bar, unsigned parity, volatile int *abort)
+{
+    for (unsigned i = 0; i < kWaitLimit; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        // a waiting warp must not take issue slots from the warps that compute
+        if (i >= 4u) __nanosleep(i < 64u ? 64u : 256u);
+        if ((i & 63u) == 63u && *abort) return false;
+    }
+    return false;
+}
+
+// The (tile, chunk) steps of one block in order: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the
+// launch.  Producer and consumers walk the same sequence independently; `g` numbers the chunks of
+// the whole sequence and selects stage (g % kTileStages) and barrier parity.
+struct TileCursor {
+    long long tile;  // current tile number
+    int prob;        // its problem
+    int rb, n0;      // row block, first column
+    int nchunks;     // ceil(K / 32)
+};
+
+__device__ __forceinline__ bool tile_cursor_load(TileCursor &tc, const TileProblem *__restrict__ problems,
+                                                 const long long *__restrict__ tile_start, int count, long long total,
+                                                 TileProblem &p)
+{
+    if (tc.tile >= total) return false;
+    int lo = tc.prob, hi = count - 1;  // tiles only move forward: the search starts at the last problem
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(tile_start + mid) <= tc.tile) lo = mid;
+        else hi = mid - 1;
+    }
+    tc.prob = lo;
+    p = problems[lo];
+    const int t = (int)(tc.tile - __ldg(tile_start + lo));
+    const int cb = t / p.row_blocks;
+    tc.rb = t - cb * p.row_blocks;
+    tc.n0 = cb * kTileN;
+    tc.nchunks = (p.K + kTileK - 1) / kTileK;
+    return true;
+}
+
+// ---- producer warp --------------------------------------------------------------------------------
+
+// Issues the B chunk starting at row k0 into stage s.  Rows past the end of B (last chunk when K is
+// not a multiple of 32) are written as zeros: the zero-filled A block multiplies every row of the
+// chunk, and stale shared memory there could hold a NaN.
 __device__ __forceinline__ void tile_load_b(TileSmem &sm, const TileProblem &p, int s, int k0, int n0, int lane)
 {
     const int cols = min(kTileN, p.N - n0);
@@ -111,240 +174,351 @@ __device__ __forceinline__ void tile_load_b(TileSmem &sm, const TileProblem &p, 
         for (int r = rows; r < kTileK; r++)
             for (int c = lane * 4; c < kTileN; c += 128)
                 *reinterpret_cast<float4 *>(&sm.Bs[s][r][c]) = make_float4(0.f, 0.f, 0.f, 0.f);
-        fence_async_smem();  // these generic-proxy writes precede later bulk copies into the same rows
-        __syncwarp();
     }
+    // generic-proxy accesses to this stage (the zeros above, the previous test pass) precede the
+    // bulk copies, which write through the async proxy
+    fence_async_smem();
+    __syncwarp();
     if (lane == 0) mbar_expect_tx(&sm.full[s], row_bytes * (unsigned)rows);
     __syncwarp();
     if (lane < rows)
         bulk_copy_g2s(&sm.Bs[s][lane][0], p.B + (size_t)(k0 + lane) * (size_t)p.N + n0, row_bytes, &sm.full[s]);
 }
 
-// Starts the asynchronous fetch of the next <= 32 entries of this warp's rows.
-__device__ __forceinline__ void tile_fetch_candidates(TileSmem &sm, const TileProblem &p, int warp, int lane)
+// True if the valid part of the chunk in stage s (rows x cols) holds an infinity or a NaN: the
+// largest magnitude bit pattern is compared with that of infinity.
+__device__ __forceinline__ bool tile_chunk_nonfinite(const TileSmem &sm, int s, int cols, int lane)
 {
-#pragma unroll
-    for (int i = 0; i < kTileRowsPerWarp; i++) {
-        const int r = warp * kTileRowsPerWarp + i;
-        const int q = sm.cursor[r] + lane;
-        if (q < sm.row_end[r]) {
-            cp_async_4(&sm.cand_col[r][lane], p.cols + q);
-            cp_async_4(&sm.cand_val[r][lane], p.values + q);
+    unsigned top = 0u;
+    const int c4 = cols >> 2;  // float4 per row that were copied (cols is a multiple of 4)
+    if (c4 == kTileN / 4) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(&sm.Bs[s][0][0]);
+#pragma unroll 8
+        for (int i = lane; i < kTileK * kTileN / 4; i += 32) {
+            const uint4 v = src[i];
+            top = max(top, max(max(v.x & 0x7fffffffu, v.y & 0x7fffffffu), max(v.z & 0x7fffffffu, v.w & 0x7fffffffu)));
+        }
+    } else {
+        for (int r = 0; r < kTileK; r++)
+            for (int c = lane; c < c4; c += 32) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(&sm.Bs[s][r][c * 4]);
+                top = max(top, max(max(v.x & 0x7fffffffu, v.y & 0x7fffffffu), max(v.z & 0x7fffffffu, v.w & 0x7fffffffu)));
+            }
+    }
+    return __any_sync(0xffffffffu, top >= 0x7f800000u);
+}
+
+// The producer's whole life: for every chunk of the block's sequence, refill a free stage; one step
+// behind, test the chunk that has landed and hand it to the consumers.  Returns false if a wait
+// ran out (after the copies still in flight have been given a bounded chance to land).
+__device__ __forceinline__ bool tile_producer(TileSmem &sm, const TileProblem *__restrict__ problems,
+                                              const long long *__restrict__ tile_start, int count, long long total,
+                                              int lane)
+{
+    volatile int *abort = &sm.abort;
+    TileCursor tc{(long long)blockIdx.x, 0, 0, 0, 0};
+    TileProblem p;
+    bool have = tile_cursor_load(tc, problems, tile_start, count, total, p);
+    int c = 0;               // chunk of the current tile to issue next
+    unsigned g = 0;          // chunks issued so far
+    int prev_cols = 0;       // columns of the chunk issued last (for its test)
+    bool ok = true;
+    while (have || g > 0) {
+        const bool issue = have;
+        int cols_now = 0;
+        if (issue) {
+            const int s = (int)(g % kTileStages);
+            if (g >= (unsigned)kTileStages)
+                ok = mbar_wait_or_abort(&sm.empty[s], ((g / kTileStages) - 1u) & 1u, abort);
+            if (!ok) break;
+            tile_load_b(sm, p, s, c * kTileK, tc.n0, lane);
+            cols_now = min(kTileN, p.N - tc.n0);
+        }
+        if (g > 0) {  // the chunk issued one step ago: wait for it, test it, release it to the consumers
+            const unsigned gp = g - 1u;
+            const int sp = (int)(gp % kTileStages);
+            ok = mbar_wait_or_abort(&sm.full[sp], (gp / kTileStages) & 1u, abort);
+            if (!ok) {
+                g = issue ? g + 1u : g;
+                break;
+            }
+            const bool bad = tile_chunk_nonfinite(sm, sp, prev_cols, lane);
+            if (lane == 0) {
+                sm.nonfinite[sp] = bad ? 1 : 0;
+                mbar_arrive(&sm.ready[sp]);  // release: the flag is visible to whoever sees the phase complete
+            }
+            __syncwarp();
+        }
+        if (!issue) break;  // that was the test of the last chunk
+        prev_cols = cols_now;
+        g++;
+        if (++c == tc.nchunks) {
+            c = 0;
+            tc.tile += gridDim.x;
+            have = tile_cursor_load(tc, problems, tile_start, count, total, p);
+        }
+    }
+    if (!ok) {
+        *abort = 1;
+        // copies that were issued but not seen to land: at most the last two chunks
+        for (unsigned back = 1; back <= 2u && back <= g; back++) {
+            const unsigned gq = g - back;
+            (void)mbar_wait(&sm.full[gq % kTileStages], (gq / kTileStages) & 1u);
+        }
+    }
+    return ok;
+}
+
+// ---- consumer warps -------------------------------------------------------------------------------
+
+// Two multiply-adds per instruction (fma.rn.f32x2, new with sm_100): the fp32 pipe does the same
+// number of them per cycle, but they take half the issue slots, which leaves room for the shared-
+// memory loads and the CSR expansion beside a busy FMA pipe.  Each half rounds exactly like fmaf
+// (the strict form keeps scalar multiplies and adds), so results do not change.
+template <bool STRICT>
+__device__ __forceinline__ float2 tmad2(float2 a, float2 b, float2 c)
+{
+    // strict: scalar multiply and add with their own roundings (the packed __fmul2_rn / __fadd2_rn
+    // pair was seen to be contracted into one packed FMA by the compiler)
+    if constexpr (STRICT) return make_float2(__fadd_rn(c.x, __fmul_rn(a.x, b.x)), __fadd_rn(c.y, __fmul_rn(a.y, b.y)));
+    else return __ffma2_rn(a, b, c);
+}
+
+// acc holds the 8 columns of one row as 4 pairs: columns (0,1) (2,3) of b0, then of b1.
+template <bool STRICT>
+__device__ __forceinline__ void row_update(float2 (&acc)[4], float av, const float4 &b0, const float4 &b1)
+{
+    const float2 a2 = make_float2(av, av);
+    acc[0] = tmad2<STRICT>(a2, make_float2(b0.x, b0.y), acc[0]);
+    acc[1] = tmad2<STRICT>(a2, make_float2(b0.z, b0.w), acc[1]);
+    acc[2] = tmad2<STRICT>(a2, make_float2(b1.x, b1.y), acc[2]);
+    acc[3] = tmad2<STRICT>(a2, make_float2(b1.z, b1.w), acc[3]);
+}
+
+// Row state of a consumer warp: lane r (< 8) holds the state of the warp's row r.
+struct TileRows {
+    int row;     // row of C (-1: the tile has no such row)
+    int cursor;  // next unconsumed entry
+    int end;     // end of the row in the CSR arrays
+};
+
+__device__ __forceinline__ void tile_rows_setup(TileRows &rs, const TileProblem &p, int rb, int warp, int lane)
+{
+    rs.row = -1;
+    rs.cursor = 0;
+    rs.end = 0;
+    if (lane < kTileRowsPerWarp) {
+        const int slot = rb * kTileM + warp * kTileRowsPerWarp + lane;
+        if (slot < p.M) {
+            rs.row = p.row_order ? __ldg(p.row_order + slot) : slot;
+            rs.cursor = __ldg(p.row_offsets + rs.row);
+            rs.end = __ldg(p.row_offsets + rs.row + 1);
         }
     }
 }
 
-// Scatters the fetched entries that fall into columns [k0, k0+32) into As[s] and writes the masks.
-// DENSE: absent entries are written as zeros, so that the inner loop can run without mask tests.
-template <bool DENSE>
-__device__ __forceinline__ void tile_expand_a(TileSmem &sm, int s, int k0, int warp, int lane)
+// Starts the asynchronous fetch of the next <= 32 entries of this warp's rows; slots past the end of
+// a row get a column that no chunk contains.
+__device__ __forceinline__ void tile_fetch_candidates(TileSmem &sm, const TileProblem &p, const TileRows &rs, int warp,
+                                                      int lane)
+{
+#pragma unroll
+    for (int r = 0; r < kTileRowsPerWarp; r++) {
+        const int q = __shfl_sync(0xffffffffu, rs.cursor, r) + lane;
+        const int e = __shfl_sync(0xffffffffu, rs.end, r);
+        if (q < e) {
+            cp_async_4(&sm.cand_col[warp][r][lane], p.cols + q);
+            cp_async_4(&sm.cand_val[warp][r][lane], p.values + q);
+        } else {
+            sm.cand_col[warp][r][lane] = 0x7fffffff;
+        }
+    }
+}
+
+// Turns the fetched entries that fall into columns [k0, k0 + 32) into the zero-filled block
+// As[warp][buf][column][row] and the presence masks, and moves the rows' cursors past them.  Columns
+// ascend, so the entries of the chunk are a prefix of the fetched ones, in column order: lane c
+// finds the value of column c at position popc(mask below c).
+__device__ __forceinline__ void tile_expand_a(TileSmem &sm, TileRows &rs, int buf, int k0, int warp, int lane)
 {
     cp_async_wait_all();
     __syncwarp();
+    float v[kTileRowsPerWarp];
+    unsigned my_mask = 0u, my_count = 0u;
 #pragma unroll
-    for (int i = 0; i < kTileRowsPerWarp; i++) {
-        const int r = warp * kTileRowsPerWarp + i;
-        const int cur = sm.cursor[r];
-        int c = -1;
-        float v = 0.f;
-        if (cur + lane < sm.row_end[r]) {
-            c = sm.cand_col[r][lane] - k0;
-            v = sm.cand_val[r][lane];
-        }
-        const bool take = (unsigned)c < (unsigned)kTileK;  // columns ascend: the taken ones are a prefix
-        if constexpr (DENSE) {
-            sm.As[s][r][lane] = 0.f;
-            __syncwarp();
-        }
-        if (take) sm.As[s][r][c] = v;
+    for (int r = 0; r < kTileRowsPerWarp; r++) {
+        const int c = sm.cand_col[warp][r][lane] - k0;
+        const float val = sm.cand_val[warp][r][lane];
+        const bool take = (unsigned)c < (unsigned)kTileK;
         const unsigned mask = __reduce_or_sync(0xffffffffu, take ? (1u << c) : 0u);
-        if (lane == 0) {
-            sm.Am[s][r] = mask;
-            sm.cursor[r] = cur + __popc(mask);
+        const float x = __shfl_sync(0xffffffffu, val, __popc(mask & ((1u << lane) - 1u)));
+        v[r] = ((mask >> lane) & 1u) ? x : 0.f;
+        if (lane == r) {
+            my_mask = mask;
+            my_count = (unsigned)__popc(mask);
         }
+    }
+    float4 *dst = reinterpret_cast<float4 *>(&sm.As[warp][buf][lane][0]);
+    dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+    dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    if (lane < kTileRowsPerWarp) {
+        sm.Am[warp][buf][lane] = my_mask;
+        rs.cursor += (int)my_count;
     }
     __syncwarp();
 }
 
+// One chunk with every entry of the 8 x 32 block multiplied (absent ones are zeros).
 template <bool STRICT>
-__device__ __forceinline__ float tmad(float a, float b, float c)
+__device__ __forceinline__ void tile_chunk_dense(const TileSmem &sm, int s, int warp, int buf, int lane,
+                                                 float2 (&acc)[kTileRowsPerWarp][4])
 {
-    if constexpr (STRICT) return __fadd_rn(c, __fmul_rn(a, b));
-    else return fmaf(a, b, c);
+    const float *bs = &sm.Bs[s][0][lane * 4];
+    const float *as = &sm.As[warp][buf][0][0];
+#pragma unroll 8
+    for (int k = 0; k < kTileK; k++) {
+        const float4 a0 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp);
+        const float4 a1 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp + 4);
+        const float4 b0 = *reinterpret_cast<const float4 *>(bs + k * kTileN);
+        const float4 b1 = *reinterpret_cast<const float4 *>(bs + k * kTileN + 128);
+        row_update<STRICT>(acc[0], a0.x, b0, b1);
+        row_update<STRICT>(acc[1], a0.y, b0, b1);
+        row_update<STRICT>(acc[2], a0.z, b0, b1);
+        row_update<STRICT>(acc[3], a0.w, b0, b1);
+        row_update<STRICT>(acc[4], a1.x, b0, b1);
+        row_update<STRICT>(acc[5], a1.y, b0, b1);
+        row_update<STRICT>(acc[6], a1.z, b0, b1);
+        row_update<STRICT>(acc[7], a1.w, b0, b1);
+    }
+}
+
+// One chunk with present entries only (used for chunks of B that hold a non-finite value, and for
+// every chunk when the masked form is asked for).
+template <bool STRICT>
+__device__ __forceinline__ void tile_chunk_masked(const TileSmem &sm, int s, int warp, int buf, int lane,
+                                                  float2 (&acc)[kTileRowsPerWarp][4])
+{
+    const float *bs = &sm.Bs[s][0][lane * 4];
+    const float *as = &sm.As[warp][buf][0][0];
+    unsigned m[kTileRowsPerWarp];
+    unsigned any = 0u;
+#pragma unroll
+    for (int i = 0; i < kTileRowsPerWarp; i++) {
+        m[i] = sm.Am[warp][buf][i];
+        any |= m[i];
+    }
+#pragma unroll 1
+    for (int k = 0; k < kTileK; k++) {
+        if (!((any >> k) & 1u)) continue;  // none of this warp's rows uses the column
+        const float4 a0 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp);
+        const float4 a1 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp + 4);
+        const float4 b0 = *reinterpret_cast<const float4 *>(bs + k * kTileN);
+        const float4 b1 = *reinterpret_cast<const float4 *>(bs + k * kTileN + 128);
+        if ((m[0] >> k) & 1u) row_update<STRICT>(acc[0], a0.x, b0, b1);
+        if ((m[1] >> k) & 1u) row_update<STRICT>(acc[1], a0.y, b0, b1);
+        if ((m[2] >> k) & 1u) row_update<STRICT>(acc[2], a0.z, b0, b1);
+        if ((m[3] >> k) & 1u) row_update<STRICT>(acc[3], a0.w, b0, b1);
+        if ((m[4] >> k) & 1u) row_update<STRICT>(acc[4], a1.x, b0, b1);
+        if ((m[5] >> k) & 1u) row_update<STRICT>(acc[5], a1.y, b0, b1);
+        if ((m[6] >> k) & 1u) row_update<STRICT>(acc[6], a1.z, b0, b1);
+        if ((m[7] >> k) & 1u) row_update<STRICT>(acc[7], a1.w, b0, b1);
+    }
 }
 
 template <bool STRICT>
-__device__ __forceinline__ void row_update(float (&acc)[8], float av, const float4 &b0, const float4 &b1)
+__device__ __forceinline__ bool tile_consumer(TileSmem &sm, const TileProblem *__restrict__ problems,
+                                              const long long *__restrict__ tile_start, int count, long long total,
+                                              bool force_masked, int warp, int lane)
 {
-    acc[0] = tmad<STRICT>(av, b0.x, acc[0]);
-    acc[1] = tmad<STRICT>(av, b0.y, acc[1]);
-    acc[2] = tmad<STRICT>(av, b0.z, acc[2]);
-    acc[3] = tmad<STRICT>(av, b0.w, acc[3]);
-    acc[4] = tmad<STRICT>(av, b1.x, acc[4]);
-    acc[5] = tmad<STRICT>(av, b1.y, acc[5]);
-    acc[6] = tmad<STRICT>(av, b1.z, acc[6]);
-    acc[7] = tmad<STRICT>(av, b1.w, acc[7]);
+    volatile int *abort = &sm.abort;
+    TileCursor tc{(long long)blockIdx.x, 0, 0, 0, 0};
+    TileProblem p;
+    unsigned g = 0;  // chunks consumed so far (the same numbering as the producer's)
+    while (tile_cursor_load(tc, problems, tile_start, count, total, p)) {
+        TileRows rs;
+        tile_rows_setup(rs, p, tc.rb, warp, lane);
+        // a warp whose 8 row slots all lie past the last row only keeps the barriers moving
+        const bool idle = tc.rb * kTileM + warp * kTileRowsPerWarp >= p.M;
+        float2 acc[kTileRowsPerWarp][4];
+#pragma unroll
+        for (int i = 0; i < kTileRowsPerWarp; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][j] = make_float2(0.f, 0.f);
+        if (!idle) {
+            tile_fetch_candidates(sm, p, rs, warp, lane);
+            tile_expand_a(sm, rs, (int)(g & 1u), 0, warp, lane);
+        }
+        for (int c = 0; c < tc.nchunks; c++, g++) {
+            const int s = (int)(g % kTileStages);
+            const int buf = (int)(g & 1u);
+            const bool more = c + 1 < tc.nchunks;
+            if (more && !idle) tile_fetch_candidates(sm, p, rs, warp, lane);  // lands while this chunk is computed
+            if (!mbar_wait_or_abort(&sm.ready[s], (g / kTileStages) & 1u, abort)) return false;
+            if (!idle) {
+                if (force_masked || sm.nonfinite[s]) tile_chunk_masked<STRICT>(sm, s, warp, buf, lane, acc);
+                else tile_chunk_dense<STRICT>(sm, s, warp, buf, lane, acc);
+                if (more) tile_expand_a(sm, rs, buf ^ 1, (c + 1) * kTileK, warp, lane);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.empty[s]);  // this warp is done with the stage
+        }
+        if (!idle) {
+#pragma unroll
+            for (int i = 0; i < kTileRowsPerWarp; i++) {
+                const int row = __shfl_sync(0xffffffffu, rs.row, i);
+                if (row >= 0) {
+                    float *crow = p.C + (size_t)row * (size_t)p.N + tc.n0;
+                    if (tc.n0 + lane * 4 < p.N)
+                        *reinterpret_cast<float4 *>(crow + lane * 4) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
+                    if (tc.n0 + 128 + lane * 4 < p.N)
+                        *reinterpret_cast<float4 *>(crow + 128 + lane * 4) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
+                }
+            }
+        }
+        tc.tile += gridDim.x;
+    }
+    return true;
 }
 
-// Persistent thread blocks pull tile numbers from `counter`; tile_start[i] is the first tile of
-// problem i.  On an mbarrier timeout error[0] is set to 1 and the block returns.
-template <bool STRICT, bool DENSE>
-__global__ void __launch_bounds__(kTileThreads, 2)
+// One thread block per SM; block b takes the tiles b, b + gridDim.x, ... (tile_start[i] is the first
+// tile of problem i; tiles of a problem are numbered column block by column block, so blocks that
+// run side by side read the same columns of B).  A tile costs ceil(K / 32) equal steps whatever its
+// pattern, and the problems are stored from the most to the least work, so this fixed deal is
+// balanced to within one tile.  On an mbarrier timeout error[0] is set to 1.
+template <bool STRICT>
+__global__ void __launch_bounds__(kTileThreads, 1)
 spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__restrict__ tile_start, int count,
-                 unsigned long long *counter, int *error)
+                 int force_masked, int *error)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     TileSmem &sm = *reinterpret_cast<TileSmem *>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wr = warp * kTileRowsPerWarp;
-
     if (tid == 0) {
-        mbar_init(&sm.full[0], 1);
-        mbar_init(&sm.full[1], 1);
+        for (int s = 0; s < kTileStages; s++) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.ready[s], 1);
+            mbar_init(&sm.empty[s], kTileConsumers);
+            sm.nonfinite[s] = 0;
+        }
         sm.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    unsigned phase0 = 0, phase1 = 0;  // parity of the next completion of each stage's barrier
     const long long total = tile_start[count];
-
-    for (;;) {
-        if (tid == 0) sm.tile = atomicAdd(counter, 1ull);
-        __syncthreads();
-        const long long tile = (long long)sm.tile;
-        if (tile >= total) break;
-        int lo = 0, hi = count - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (__ldg(tile_start + mid) <= tile) lo = mid;
-            else hi = mid - 1;
-        }
-        const TileProblem p = problems[lo];
-        const int t = (int)(tile - __ldg(tile_start + lo));
-        const int cb = t / p.row_blocks, rb = t - cb * p.row_blocks;
-        const int n0 = cb * kTileN;
-
-        if (tid < kTileM) {
-            const int slot = rb * kTileM + tid;
-            int row = -1, cur = 0, end = 0;
-            if (slot < p.M) {
-                row = p.row_order ? __ldg(p.row_order + slot) : slot;
-                cur = __ldg(p.row_offsets + row);
-                end = __ldg(p.row_offsets + row + 1);
-            }
-            sm.row_id[tid] = row;
-            sm.cursor[tid] = cur;
-            sm.row_end[tid] = end;
-        }
-        __syncthreads();
-
-        float acc[kTileRowsPerWarp][8];
-#pragma unroll
-        for (int i = 0; i < kTileRowsPerWarp; i++)
-#pragma unroll
-            for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
-
-        const int nchunks = (p.K + kTileK - 1) / kTileK;
-        if (warp == 0) tile_load_b(sm, p, 0, 0, n0, lane);
-        tile_fetch_candidates(sm, p, warp, lane);
-        tile_expand_a<DENSE>(sm, 0, 0, warp, lane);
-
-        bool aborted = false;
-        for (int c = 0; c < nchunks; c++) {
-            const int s = c & 1;
-            const bool more = c + 1 < nchunks;
-            if (more) {
-                if (warp == 0) tile_load_b(sm, p, s ^ 1, (c + 1) * kTileK, n0, lane);
-                tile_fetch_candidates(sm, p, warp, lane);  // lands while this chunk is computed
-            }
-            const unsigned parity = s ? phase1 : phase0;
-            // A thread whose wait runs out raises the flag and still walks to the barrier below,
-            // so that the whole block leaves together.
-            if (!mbar_wait(&sm.full[s], parity)) *(volatile int *)&sm.abort = 1;
-            if (s) phase1 ^= 1u;
-            else phase0 ^= 1u;
-
-            if constexpr (DENSE) {
-                // every entry of the 8 x 32 block is multiplied; absent ones are zeros
-#pragma unroll 2
-                for (int k4 = 0; k4 < kTileK; k4 += 4) {
-                    float4 a[kTileRowsPerWarp];
-#pragma unroll
-                    for (int i = 0; i < kTileRowsPerWarp; i++) a[i] = *reinterpret_cast<const float4 *>(&sm.As[s][wr + i][k4]);
-#pragma unroll
-                    for (int kk = 0; kk < 4; kk++) {
-                        const float4 b0 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][lane * 4]);
-                        const float4 b1 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][128 + lane * 4]);
-#pragma unroll
-                        for (int i = 0; i < kTileRowsPerWarp; i++) {
-                            const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
-                            row_update<STRICT>(acc[i], av, b0, b1);
-                        }
-                    }
-                }
-            } else {
-            unsigned m[kTileRowsPerWarp];
-            unsigned any = 0;
-#pragma unroll
-            for (int i = 0; i < kTileRowsPerWarp; i++) {
-                m[i] = sm.Am[s][wr + i];
-                any |= m[i];
-            }
-#pragma unroll 1
-            for (int k4 = 0; k4 < kTileK; k4 += 4) {
-                const unsigned any4 = (any >> k4) & 0xFu;
-                if (any4 == 0u) continue;  // none of this warp's rows uses these four columns
-                float4 a[kTileRowsPerWarp];
-                unsigned mk[kTileRowsPerWarp];
-#pragma unroll
-                for (int i = 0; i < kTileRowsPerWarp; i++) {
-                    a[i] = *reinterpret_cast<const float4 *>(&sm.As[s][wr + i][k4]);
-                    mk[i] = m[i] >> k4;
-                }
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    if ((any4 >> kk) & 1u) {
-                        const float4 b0 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][lane * 4]);
-                        const float4 b1 = *reinterpret_cast<const float4 *>(&sm.Bs[s][k4 + kk][128 + lane * 4]);
-#pragma unroll
-                        for (int i = 0; i < kTileRowsPerWarp; i++) {
-                            const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
-                            if (mk[i] & (1u << kk)) row_update<STRICT>(acc[i], av, b0, b1);
-                        }
-                    }
-                }
-            }
-            }
-            if (more) tile_expand_a<DENSE>(sm, s ^ 1, (c + 1) * kTileK, warp, lane);
-            __syncthreads();  // every warp is done with Bs[s]: it may be refilled in the next round
-            if (*(volatile int *)&sm.abort) {
-                aborted = true;
-                break;
-            }
-        }
-        if (aborted) {
-            // Record the failure, give the copies still in flight one more bounded chance to land
-            // in this block's shared memory, and leave without storing the tile.
-            if (tid == 0) {
-                atomicExch(error, 1);
-                (void)mbar_wait(&sm.full[0], phase0);
-                (void)mbar_wait(&sm.full[1], phase1);
-            }
-            __syncthreads();
-            return;
-        }
-
-#pragma unroll
-        for (int i = 0; i < kTileRowsPerWarp; i++) {
-            const int row = sm.row_id[wr + i];
-            if (row >= 0) {
-                float *crow = p.C + (size_t)row * (size_t)p.N + n0;
-                if (n0 + lane * 4 < p.N)
-                    *reinterpret_cast<float4 *>(crow + lane * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-                if (n0 + 128 + lane * 4 < p.N)
-                    *reinterpret_cast<float4 *>(crow + 128 + lane * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-            }
-        }
+    // Registers move from the producer's group of four warps to the consumers (the block is launched
+    // with 96 per thread): the producer's loop needs few, the consumers hold 64 accumulators each.
+    bool ok = true;
+    if (warp >= kTileConsumers) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        // the producer and the three spare warps of its group, which leave at once
+        if (warp == kTileConsumers) ok = tile_producer(sm, problems, tile_start, count, total, lane);
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        ok = tile_consumer<STRICT>(sm, problems, tile_start, count, total, force_masked != 0, warp, lane);
+    }
+    if (!ok) {
+        *(volatile int *)&sm.abort = 1;
+        if (lane == 0) atomicExch(error, 1);
     }
 }
 

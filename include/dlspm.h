@@ -189,6 +189,45 @@ int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_problem *probl
 int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                                   void *stream);
 
+/* ---- grouped launches over many independent SDDMMs / fused chains --------------------------- */
+
+typedef struct dlspm_sddmm_problem {
+    int M, K, N, nnz;          /* N = inner (dot) dimension                                   */
+    const int *row_offsets;    /* device */
+    const int *column_indices; /* device */
+    const float *mask_values;  /* device, nnz factors, or NULL = 1.0 (the reference's behaviour) */
+    const float *lhs;          /* device, M x N */
+    const float *rhs;          /* device, K x N */
+    float *out_values;         /* device, nnz   */
+} dlspm_sddmm_problem;
+
+typedef struct dlspm_fused_problem {
+    int M, K, N, nnz;
+    const int *row_offsets;    /* device */
+    const int *column_indices; /* device */
+    const float *C;            /* device, M x N */
+    const float *B;            /* device, K x N */
+    const float *D;            /* device, K x N */
+    float *E;                  /* device, M x N */
+} dlspm_fused_problem;
+
+/* Runs `count` independent SDDMMs (each as dlspm_sddmm_csr_masked_f32 would) in one persistent
+ * launch per register layout present in the batch (the layout follows from N: at most six, one for
+ * a batch with a single inner dimension).  Replaces the per-matrix process launches of
+ * SDDMM/batch-run-sddmm_fromfile:31-47, where every layer-sized pattern is launch-bound on its own.
+ * `problems` is a HOST array; the tables go to the context's scratch, so the same rules as for
+ * dlspm_spmm_batched_f32 hold: calls on one context ordered on one stream, not on a capturing
+ * stream.  Problems whose N or pointers rule out 128-bit loads, or with N > 1024, are run one by
+ * one with the single-matrix kernels inside the same call. */
+int dlspm_sddmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems, void *stream);
+/* The same for the fused SDDMM -> SpMM chain (each problem as dlspm_fused_sddmm_spmm_f32 would);
+ * replaces the per-matrix runs of FUSED/batch-run-fused:22-34. */
+int dlspm_fused_batched_f32(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems, void *stream);
+/* Host-pointer forms: every array of every problem is copied in, the grouped launch runs, results
+ * are copied back; returns when they are on the host. */
+int dlspm_sddmm_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems);
+int dlspm_fused_batched_f32_host(dlspm_ctx *ctx, int count, const dlspm_fused_problem *problems);
+
 /* A prepared batch: the problem table and its tile index live on the device, so repeated
  * launches cost no host work.  Creating it also analyses the patterns on the device: rows are
  * ordered by length inside every problem (so that the warps of a tile finish together), and
@@ -374,6 +413,10 @@ int dlspm_selftest_bounded_wait(dlspm_ctx *ctx, unsigned polls, int *timed_out);
 /* Sustained fp32 FMA rate of the device in TFLOP/s (a register-only FMA loop over all SMs); the
  * denominator of the compute term of the roofline. */
 int dlspm_measure_fp32_peak(dlspm_ctx *ctx, double *tflops);
+/* The same figure twice: with one multiply-add per instruction (as above) and with the packed form
+ * (two per instruction, fma.rn.f32x2).  Both run on the same fp32 lanes; the pair shows whether the
+ * packed form changes the arithmetic peak or only the number of issue slots it needs. */
+int dlspm_measure_fp32_peaks(dlspm_ctx *ctx, double *scalar_tflops, double *packed_tflops);
 
 #ifdef __cplusplus
 }

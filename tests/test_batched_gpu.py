@@ -373,6 +373,40 @@ def test_zero_filled_tiles_do_not_see_stale_rows(pkg, oracle, ctx, dev):
     assert (got == got[0]).all()
 
 
+def test_non_finite_rows_of_b_reach_only_the_rows_that_reference_them(pkg, oracle, ctx, dev):
+    """The zero-filled tiled kernel multiplies absent entries as zeros, and 0 * inf is NaN: chunks of
+    B that hold a non-finite value must therefore run under the presence masks.  One row of B that
+    no row of A references is all infinities, another that some rows reference holds a NaN and an
+    infinity: the result has the bits of the row-gather kernel, and rows that reference neither stay
+    finite, as in the reference host loop."""
+    M, K, N = 300, 200, 512
+    ro, ci = csr_rowlen_normal(pkg, M, K, 0.5, 4242)
+    unused, used = 77, 130
+    keep = ci != unused                      # drop column 77 from every row
+    lengths = np.add.reduceat(keep.astype(np.int64), ro[:-1]) * (np.diff(ro) > 0)
+    ci = ci[keep]
+    ro = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    vals = pkg.gen_dense_host(int(ci.size), 4242, 2)
+    B = dense(pkg, K, N, 4242, 10).copy()
+    B[unused, :] = np.inf
+    B[used, 5] = np.nan
+    B[used, 300] = -np.inf
+    probs = [(M, K, N, ro, ci, vals, B)]
+    gather, _ = _run_prepared(pkg, ctx, dev, probs, pkg.SPMM_KERNEL_GATHER)
+    for choice in (pkg.SPMM_KERNEL_TILED_DENSE, pkg.SPMM_KERNEL_TILED):
+        tiled, info = _run_prepared(pkg, ctx, dev, probs, choice)
+        assert info[1] == 1 and info[2] == 0
+        assert np.array_equal(tiled[0].view(np.uint32), gather[0].view(np.uint32))
+    out = gather[0].reshape(M, N)
+    refs_used = np.array([used in ci[ro[i]:ro[i + 1]] for i in range(M)])
+    assert refs_used.any() and not refs_used.all()
+    assert np.isfinite(out[~refs_used]).all()
+    assert np.isnan(out[refs_used][:, 5]).all() and np.isinf(out[refs_used][:, 300]).all()
+    fin = np.ones(N, dtype=bool)
+    fin[[5, 300]] = False
+    assert np.isfinite(out[:, fin]).all()
+
+
 def test_tiled_kernel_strict_mode_is_bit_exact(pkg, oracle, ctx, dev):
     probs = tiled_cases(pkg)[:4]
     ctx.set_option(pkg.OPT_STRICT_FP32, 1)
