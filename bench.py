@@ -646,6 +646,66 @@ def run_extras(pkg, ctx, dev, hbm_gbs, fp32_tflops, reps=20):
         "binds": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (fp32_tflops * 1e12) else "fp32"}
     batch.close()
 
+    # SDDMM and the fused chain on the same 90 % sparsity grid (mask shapes of the sweep, inner
+    # dimension 32 / 128 / 256): lone launches, then 24 copies of every case in one grouped call
+    inner = [32, 128, 256]
+
+    def sddmm_bytes(M, K, N, nnz):
+        return 4 * (M + 1) + 8 * nnz + 4 * M * N + 4 * K * N
+
+    def fused_bytes(M, K, N, nnz):
+        return 4 * (M + 1) + 4 * nnz + 4 * N * (M + 2 * K) + 4 * M * N
+
+    for op in ("sddmm", "fused"):
+        lone = {}
+        copies = 24
+        arr = pkg.RowProblemArray(op, 15 * copies)
+        flops = nbytes = 0.0
+        idx = 0
+        for (M, K) in SHAPES:
+            for N in inner:
+                for c in range(copies):
+                    seed = 80000 + 100 * idx + c
+                    ro = pkg.gen_rowlen_normal_host(M, K, 0.9, COV, seed)
+                    nnz = int(ro[-1])
+                    d_ro = up(ro)
+                    d_ci = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)[:nnz]
+                    ctx.gen_sample_columns(M, K, d_ro, seed, d_ci)
+                    a = torch.empty(M * N, device=dev)
+                    ctx.gen_dense(a, seed, 11, kind=2)
+                    b = torch.empty(K * N, device=dev)
+                    ctx.gen_dense(b, seed, 12, kind=2)
+                    if op == "sddmm":
+                        o = torch.empty(max(nnz, 1), device=dev)[:nnz]
+                        arr.set_sddmm(idx * copies + c, M, K, N, nnz, d_ro, d_ci, a, b, o)
+                        fl, by = 2.0 * nnz * N, sddmm_bytes(M, K, N, nnz)
+                        fn = (lambda M=M, K=K, N=N, nnz=nnz, t=(d_ro, d_ci, a, b, o): ctx.sddmm(M, K, N, nnz, *t))
+                    else:
+                        dv = torch.empty(K * N, device=dev)
+                        ctx.gen_dense(dv, seed, 13, kind=2)
+                        o = torch.empty(M * N, device=dev)
+                        arr.set_fused(idx * copies + c, M, K, N, nnz, d_ro, d_ci, a, b, dv, o)
+                        fl, by = 4.0 * nnz * N, fused_bytes(M, K, N, nnz)
+                        fn = (lambda M=M, K=K, N=N, nnz=nnz, t=(d_ro, d_ci, a, b, dv, o): ctx.fused(M, K, N, nnz, *t))
+                    flops += fl
+                    nbytes += by
+                    if c == 0:
+                        fn(); fn()
+                        lone[f"{M}x{K}_n{N}"] = summarize(time_graph(fn), time_kernel(fn, 10, flush), fl, by, hbm_gbs, fp32_tflops)
+                idx += 1
+        out[f"{op}_sweep_s0.9"] = lone
+        call = (lambda: ctx.sddmm_batched(arr)) if op == "sddmm" else (lambda: ctx.fused_batched(arr))
+        call()
+        torch.cuda.synchronize()
+        ms = st.median(time_kernel(call, 7))
+        out[f"{op}_sweep_s0.9_batched"] = {
+            "problems": 15 * copies, "ms_median": ms, "us_per_problem": ms * 1e3 / (15 * copies), "gflops": flops / ms * 1e-6,
+            "hbm_gbs": nbytes / ms * 1e-6, "hbm_frac": nbytes / ms * 1e-6 / hbm_gbs,
+            "roof_frac": max(nbytes / (hbm_gbs * 1e9), flops / (fp32_tflops * 1e12)) * 1e3 / ms,
+            "binds": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (fp32_tflops * 1e12) else "fp32",
+            "note": "one dlspm_%s_batched_f32 call: table build and copy included, three launches (one per inner dimension)" % op}
+        del arr
+
     # shapes whose algorithmic intensity is below the fp32 ridge (HBM-bound on paper), many copies
     # of one shape in a grouped launch, about 1.5 GB resident each
     small = {}

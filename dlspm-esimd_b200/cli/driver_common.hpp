@@ -38,7 +38,16 @@ struct Options {
     bool attention = false;      // fused driver: scale (and softmax) between the two products
     bool softmax = false;
     float scale = 1.f;
+    int check_rows = 0;          // > 0: the host loop checks about this many evenly spaced rows only
+    std::string list;            // from-file drivers: a file of "<pattern file> <batchsize>" lines, all run by one process
 };
+
+// Distance between checked rows: 1 = every row.
+inline int check_stride(const Options &o, int M)
+{
+    if (o.check_rows <= 0 || o.check_rows >= M) return 1;
+    return (M + o.check_rows - 1) / o.check_rows;
+}
 
 inline Options parse(int argc, char **argv)
 {
@@ -58,6 +67,8 @@ inline Options parse(int argc, char **argv)
         else if (a == "--graph") o.graph = true;
         else if (a == "--softmax") o.attention = o.softmax = true;
         else if (a == "--scale") { o.attention = true; o.scale = (float)atof(next()); }
+        else if (a == "--check-rows") o.check_rows = atoi(next());
+        else if (a == "--list") o.list = next();
         else o.positional.push_back(a);
     }
     return o;
@@ -179,9 +190,10 @@ int time_launches(F &&launch, int reps, float *flush, size_t flush_elems, double
 // ---- verification loops (print-only) -----------------------------------------------------------
 
 // fp32 accumulation in CSR order, the reference's Spmm (SPMM/spmm-esimd-fromfile.cpp:63-83).
-inline void check_spmm(const float *a, const int *ro, const int *ci, const float *b, float *c, int M, int N)
+// (stride > 1: only rows 0, stride, 2*stride, ... are computed; the others are left as they are)
+inline void check_spmm(const float *a, const int *ro, const int *ci, const float *b, float *c, int M, int N, int stride = 1)
 {
-    for (int i = 0; i < M; ++i)
+    for (int i = 0; i < M; i += stride)
         for (int j = 0; j < N; ++j) {
             float acc = 0.0f;
             for (int l = ro[i]; l < ro[i + 1]; l++) acc += a[l] * b[(size_t)ci[l] * N + j];
@@ -190,9 +202,9 @@ inline void check_spmm(const float *a, const int *ro, const int *ci, const float
 }
 
 // double accumulation, the reference's Sddmm (SDDMM/sddmm-esimd-fromfile_v4.cpp:18-36).
-inline void check_sddmm(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M, int N)
+inline void check_sddmm(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M, int N, int stride = 1)
 {
-    for (int i = 0; i < M; ++i)
+    for (int i = 0; i < M; i += stride)
         for (int j = ro[i]; j < ro[i + 1]; ++j) {
             double acc = 0.0;
             for (int l = 0; l < N; ++l) acc += (double)lhs[(size_t)i * N + l] * (double)rhs[(size_t)ci[j] * N + l];
@@ -201,9 +213,9 @@ inline void check_sddmm(const int *ro, const int *ci, const float *lhs, const fl
 }
 
 // double accumulation, the Spmm of the fused reference (FUSED/fused.cpp:67-89).
-inline void check_spmm_f64(const float *a, const int *ro, const int *ci, const float *d, float *e, int M, int N)
+inline void check_spmm_f64(const float *a, const int *ro, const int *ci, const float *d, float *e, int M, int N, int stride = 1)
 {
-    for (int i = 0; i < M; ++i)
+    for (int i = 0; i < M; i += stride)
         for (int j = 0; j < N; ++j) {
             double acc = 0.0;
             for (int l = ro[i]; l < ro[i + 1]; ++l) acc += (double)a[l] * (double)d[(size_t)ci[l] * N + j];
@@ -226,6 +238,24 @@ inline Diff compare(const float *cpu, const float *gpu, size_t n)
         if (diff > d.max_diff) {
             d.max_diff = diff;
             d.maxi = i;
+        }
+    }
+    return d;
+}
+
+// The same over the checked rows only: row i covers elements [begin(i), end(i)).
+template <class Begin, class End>
+Diff compare_rows(const float *cpu, const float *gpu, int M, int stride, Begin begin, End end)
+{
+    Diff d;
+    for (int i = 0; i < M; i += stride) {
+        const size_t b = begin(i), e = end(i);
+        if (e <= b) continue;
+        const Diff r = compare(cpu + b, gpu + b, e - b);
+        d.max_rel_diff = std::max(d.max_rel_diff, r.max_rel_diff);
+        if (r.max_diff > d.max_diff) {
+            d.max_diff = r.max_diff;
+            d.maxi = b + r.maxi;
         }
     }
     return d;
@@ -262,8 +292,9 @@ inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, 
     dlspm_gen_dense_host(B.data(), B.size(), o.seed, 10, 0, kind);
     printf("rhs_matrix allocated\n");
     if (o.check) {
-        Ccpu.resize((size_t)M * N);
-        check_spmm(vals.data(), ro.data(), ci.data(), B.data(), Ccpu.data(), M, N);
+        Ccpu.assign((size_t)M * N, 0.f);
+        check_spmm(vals.data(), ro.data(), ci.data(), B.data(), Ccpu.data(), M, N, check_stride(o, M));
+        if (check_stride(o, M) > 1) printf("host check on every %d-th row\n", check_stride(o, M));
         printf("checksum_cpu = %.7g\n", mean_square(Ccpu.data(), Ccpu.size()));
     }
     int *d_ro = to_device(ro), *d_ci = to_device(ci);
@@ -319,7 +350,8 @@ inline int run_spmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N, 
     printf("checksum_gpu = %.7g\n", mean_square(C.data(), C.size()));
     Diff d;
     if (o.check) {
-        d = compare(Ccpu.data(), C.data(), C.size());
+        d = compare_rows(Ccpu.data(), C.data(), M, check_stride(o, M), [&](int i) { return (size_t)i * N; },
+                         [&](int i) { return (size_t)(i + 1) * N; });
         printf("maxi = %zu max_diff = %g max_rel_diff = %g\n", d.maxi, d.max_diff, d.max_rel_diff);
         if (!C.empty()) {
             printf("output_cpu[%zu] = %.7g\n", d.maxi, Ccpu[d.maxi]);
@@ -348,8 +380,9 @@ inline int run_sddmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     dlspm_gen_dense_host(lhs.data(), lhs.size(), o.seed, 11, 0, kind);
     dlspm_gen_dense_host(rhs.data(), rhs.size(), o.seed, 12, 0, kind);
     if (o.check) {
-        out_cpu.resize((size_t)nnz);
-        check_sddmm(ro.data(), ci.data(), lhs.data(), rhs.data(), out_cpu.data(), M, N);
+        out_cpu.assign((size_t)nnz, 0.f);
+        check_sddmm(ro.data(), ci.data(), lhs.data(), rhs.data(), out_cpu.data(), M, N, check_stride(o, M));
+        if (check_stride(o, M) > 1) printf("host check on every %d-th row\n", check_stride(o, M));
     }
     int *d_ro = to_device(ro), *d_ci = to_device(ci);
     float *d_l = to_device(lhs), *d_r = to_device(rhs), *d_o = to_device(out);
@@ -388,7 +421,8 @@ inline int run_sddmm_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     if (o.check) {
         printf("checksum_cpu = %.7g\n", mean_square(out_cpu.data(), out_cpu.size()));
         printf("checksum_gpu = %.7g\n", mean_square(out.data(), out.size()));
-        d = compare(out_cpu.data(), out.data(), out.size());
+        d = compare_rows(out_cpu.data(), out.data(), M, check_stride(o, M), [&](int i) { return (size_t)ro[(size_t)i]; },
+                         [&](int i) { return (size_t)ro[(size_t)i + 1]; });
         printf("maxi = %zu max_diff = %g\n", d.maxi, d.max_diff);
         if (nnz) {
             printf("output_cpu[%zu] = %.7g\n", d.maxi, out_cpu[d.maxi]);
@@ -424,7 +458,11 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     if (o.check) {
         a_values.resize((size_t)nnz);
         e_gold.resize((size_t)M * N);
-        check_sddmm(ro.data(), ci.data(), c.data(), b.data(), a_values.data(), M, N);
+        const int stride = check_stride(o, M);
+        if (stride > 1) printf("host check on every %d-th row\n", stride);
+        std::fill(a_values.begin(), a_values.end(), 0.f);
+        std::fill(e_gold.begin(), e_gold.end(), 0.f);
+        check_sddmm(ro.data(), ci.data(), c.data(), b.data(), a_values.data(), M, N, stride);
         printf("checksum_a_values = %f\n", sqrt(mean_square(a_values.data(), a_values.size())));
         if (o.attention) {  // weights from the sampled products: scale, then softmax over each row
             for (int i = 0; i < M; i++) {
@@ -439,7 +477,7 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
                     for (int p = ro[(size_t)i]; p < ro[(size_t)i + 1]; p++) a_values[(size_t)p] = (float)(a_values[(size_t)p] / sum);
             }
         }
-        check_spmm_f64(a_values.data(), ro.data(), ci.data(), dd.data(), e_gold.data(), M, N);
+        check_spmm_f64(a_values.data(), ro.data(), ci.data(), dd.data(), e_gold.data(), M, N, stride);
         printf("checksum_e = %f\n", sqrt(mean_square(e_gold.data(), e_gold.size())));
     }
     int *d_ro = to_device(ro), *d_ci = to_device(ci);
@@ -476,7 +514,8 @@ inline int run_fused_case(dlspm_ctx *ctx, const Options &o, int M, int K, int N,
     printf("checksum_e using gpu = %f\n", sqrt(mean_square(e.data(), e.size())));
     Diff d;
     if (o.check) {
-        d = compare(e_gold.data(), e.data(), e.size());
+        d = compare_rows(e_gold.data(), e.data(), M, check_stride(o, M), [&](int i) { return (size_t)i * N; },
+                         [&](int i) { return (size_t)(i + 1) * N; });
         printf("maxi = %zu max_diff = %g\n", d.maxi, d.max_diff);
         if (!e.empty()) {
             printf("gold output[%zu] = %.7g\n", d.maxi, e_gold[d.maxi]);
@@ -557,6 +596,21 @@ inline int load_smtx(const std::string &path, int N, int *M, int *K, std::vector
             printf("wrote %s\n", bin.c_str());
     }
     return rc;
+}
+
+// Lines "<pattern file> <batchsize>" of a list file (for --list: one process, one context, many files).
+inline bool read_list(const std::string &path, std::vector<std::pair<std::string, int>> &items)
+{
+    FILE *f = fopen(path.c_str(), "r");
+    if (!f) {
+        printf("Error opening file!\n");
+        return false;
+    }
+    char name[4096];
+    int n = 0;
+    while (fscanf(f, "%4095s %d", name, &n) == 2) items.emplace_back(name, n);
+    fclose(f);
+    return true;
 }
 
 }  // namespace drv

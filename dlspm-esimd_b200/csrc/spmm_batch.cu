@@ -28,7 +28,7 @@ struct BatchProblem {
     int K;
     const int *row_order;  // rows from the longest to the shortest (nullptr: natural order)
     int nnz;
-    int pad;
+    int rows_per_tile;  // 8 (one row per warp) or 64 (each warp walks eight rows, served by the coarse launch)
 };
 
 template <int VEC, bool STRICT>
@@ -45,10 +45,24 @@ __device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, in
         spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
 }
 
+constexpr int kCoarseRows = 8 * kWarpsPerCta;  // rows per tile of the coarse launch
+
+template <bool STRICT>
+__device__ __forceinline__ void batched_row(const BatchProblem &p, int slab, int slot, int lane, int2 *stage)
+{
+    const int row = p.row_order ? __ldg(p.row_order + slot) : slot;
+    const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+    if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage);
+    else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage);
+    else batched_tile<1, STRICT>(p, slab, row, start, end, lane, stage);
+}
+
 // Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
 // tile of problem i (problems are stored from the most to the least work), tile_start[count] the
 // total.
-template <bool STRICT>
+// COARSE: the tiles of this launch cover 64 rows (each warp walks eight of them) instead of 8; a
+// build of its own, because the extra loop costs the common build registers it does not have.
+template <bool STRICT, bool COARSE>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *__restrict__ tile_start,
                     int count, unsigned long long *counter)
@@ -72,13 +86,14 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
         const BatchProblem p = problems[lo];
         const long long t = tile - __ldg(tile_start + lo);
         const int slab = (int)(t / p.row_groups);
-        const int slot = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
-        if (slot < p.M) {
-            const int row = p.row_order ? __ldg(p.row_order + slot) : slot;
-            const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
-            if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage[warp]);
-            else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage[warp]);
-            else batched_tile<1, STRICT>(p, slab, row, start, end, lane, stage[warp]);
+        if constexpr (COARSE) {
+            const int first = (int)(t - (long long)slab * p.row_groups) * kCoarseRows;
+            const int last = min(first + kCoarseRows, p.M);
+#pragma unroll 1
+            for (int slot = first + warp; slot < last; slot += kWarpsPerCta) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
+        } else {
+            const int slot = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
+            if (slot < p.M) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
         }
     }
 }
@@ -87,8 +102,36 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
 
 namespace {
 
+// Rows per tile of a problem.  A tile of eight rows with a handful of nonzeros each moves a few
+// KiB, less than the latency chain of drawing it costs, so the grouped launch reached only 46 to
+// 62 % of the HBM rate on batches of small, very sparse problems; with 64 rows per tile that
+// overhead is paid an eighth as often.  Long rows keep 8 rows per tile (their tiles are large enough,
+// and finer tiles balance better).
+inline int rows_per_tile_for(const dlspm_problem &q, bool allow_coarse)
+{
+    if (!allow_coarse || q.M <= kWarpsPerCta) return kWarpsPerCta;
+    return (double)q.nnz <= 32.0 * (double)q.M ? kCoarseRows : kWarpsPerCta;
+}
+
+// (One-chunk slabs for such problems, so that the slab of B would stay in L1 for the 64 rows of a
+// tile, were measured and lost: 0.87 -> 0.50 of the HBM rate on 64 x 64 at 2 %, N = 1024.)
+// Coarse tiles are used only when the batch still yields several tiles per resident thread block
+// with them; a small batch keeps the finest tiling so that it fills the device.
+bool coarse_tiles_pay(const dlspm_ctx *ctx, int count, const dlspm_problem *problems)
+{
+    long long tiles = 0;
+    for (int i = 0; i < count; i++) {
+        const dlspm_problem &q = problems[i];
+        if (q.M <= 0 || q.N <= 0) continue;
+        const int vec = dlspm_vec_width(q.N, q.B, q.C);
+        const int slabs = dlspm_ceil_div(q.N, 32 * vec * spmm_slab_chunks(q.N, vec));
+        tiles += (long long)dlspm_ceil_div(q.M, rows_per_tile_for(q, true)) * slabs;
+    }
+    return tiles >= 4LL * 8 * ctx->sm_count;
+}
+
 // Table entry of one problem (natural row order).
-BatchProblem make_batch_problem(const dlspm_problem &q)
+BatchProblem make_batch_problem(const dlspm_problem &q, bool allow_coarse)
 {
     BatchProblem b;
     b.values = q.values;
@@ -98,13 +141,13 @@ BatchProblem make_batch_problem(const dlspm_problem &q)
     b.C = q.C;
     b.M = q.M;
     b.N = q.N;
-    b.row_groups = dlspm_ceil_div(q.M, kWarpsPerCta);
+    b.rows_per_tile = rows_per_tile_for(q, allow_coarse);
+    b.row_groups = dlspm_ceil_div(q.M, b.rows_per_tile);
     b.vec = dlspm_vec_width(q.N, q.B, q.C);
     b.chunks = spmm_slab_chunks(q.N, b.vec);
     b.K = q.K;
     b.row_order = nullptr;
     b.nnz = q.nnz;
-    b.pad = 0;
     return b;
 }
 
@@ -130,9 +173,42 @@ int reject_capturing_stream(dlspm_ctx *ctx, cudaStream_t st, const char *who)
     return DLSPM_OK;
 }
 
+// How a table of row-gather problems is cut between the two launches: the first `fine` entries have
+// tiles of 8 rows, the `coarse` ones after them tiles of 64 rows.  The tile index holds the fine
+// part (fine + 1 entries) followed by the coarse part (coarse + 1 entries).
+struct GatherSplit {
+    int fine, coarse;
+    long long tiles_fine, tiles_coarse;
+};
+
+// Orders a table (already sorted by decreasing work) fine problems first and builds its tile index.
+void finish_gather_tables(std::vector<BatchProblem> &tab, std::vector<long long> &starts, GatherSplit &split)
+{
+    std::stable_partition(tab.begin(), tab.end(), [](const BatchProblem &b) { return b.rows_per_tile == kWarpsPerCta; });
+    starts.clear();
+    split = GatherSplit{0, 0, 0, 0};
+    for (const BatchProblem &b : tab) split.fine += b.rows_per_tile == kWarpsPerCta ? 1 : 0;
+    split.coarse = (int)tab.size() - split.fine;
+    long long run = 0;
+    for (int i = 0; i < split.fine; i++) {
+        const BatchProblem &b = tab[(size_t)i];
+        starts.push_back(run);
+        run += (long long)b.row_groups * dlspm_ceil_div(b.N, 32 * b.vec * b.chunks);
+    }
+    starts.push_back(run);
+    split.tiles_fine = run;
+    run = 0;
+    for (size_t i = (size_t)split.fine; i < tab.size(); i++) {
+        starts.push_back(run);
+        run += (long long)tab[i].row_groups * dlspm_ceil_div(tab[i].N, 32 * tab[i].vec * tab[i].chunks);
+    }
+    starts.push_back(run);
+    split.tiles_coarse = run;
+}
+
 // Builds the host-side tables for a batch: problems ordered by decreasing nnz*N.
-int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProblem> &tab,
-                 std::vector<long long> &starts)
+int build_tables(const dlspm_ctx *ctx, int count, const dlspm_problem *problems, std::vector<BatchProblem> &tab,
+                 std::vector<long long> &starts, GatherSplit &split)
 {
     std::vector<int> order;
     order.reserve(count);
@@ -147,16 +223,9 @@ int build_tables(int count, const dlspm_problem *problems, std::vector<BatchProb
         return (double)problems[x].nnz * problems[x].N > (double)problems[y].nnz * problems[y].N;
     });
     tab.clear();
-    starts.clear();
-    long long run = 0;
-    for (int i : order) {
-        const dlspm_problem &q = problems[i];
-        const BatchProblem b = make_batch_problem(q);
-        starts.push_back(run);
-        run += (long long)b.row_groups * dlspm_ceil_div(q.N, 32 * b.vec * b.chunks);
-        tab.push_back(b);
-    }
-    starts.push_back(run);
+    const bool coarse = coarse_tiles_pay(ctx, count, problems);
+    for (int i : order) tab.push_back(make_batch_problem(problems[i], coarse));
+    finish_gather_tables(tab, starts, split);
     return DLSPM_OK;
 }
 
@@ -228,9 +297,9 @@ struct dlspm_batch {
     dlspm_ctx *ctx;
     // row-gather part
     int count;
-    long long tiles;
+    GatherSplit split;            // fine and coarse launches over `problems`
     BatchProblem *problems;       // device
-    long long *tile_start;        // device, count + 1
+    long long *tile_start;        // device, count + 2 (fine part, coarse part)
     // tiled part (denser problems)
     int tcount;
     long long ttiles;
@@ -244,15 +313,25 @@ struct dlspm_batch {
 
 namespace {
 
+// d_counter: two work counters (fine launch, coarse launch).
 int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long long *d_starts,
-                        unsigned long long *d_counter, int count, long long tiles, cudaStream_t st)
+                        unsigned long long *d_counter, const GatherSplit &split, cudaStream_t st)
 {
-    if (count == 0 || tiles == 0) return DLSPM_OK;
-    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, sizeof(unsigned long long), st));
-    const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * 8);
-    dim3 grid((unsigned)want), block(kWarpsPerCta * 32);
-    if (ctx->strict_fp32) spmm_batched_kernel<true><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
-    else spmm_batched_kernel<false><<<grid, block, 0, st>>>(d_tab, d_starts, count, d_counter);
+    if (split.tiles_fine == 0 && split.tiles_coarse == 0) return DLSPM_OK;
+    DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, 2 * sizeof(unsigned long long), st));
+    dim3 block(kWarpsPerCta * 32);
+    if (split.fine > 0 && split.tiles_fine > 0) {
+        dim3 grid((unsigned)std::min<long long>(split.tiles_fine, (long long)ctx->sm_count * 8));
+        if (ctx->strict_fp32) spmm_batched_kernel<true, false><<<grid, block, 0, st>>>(d_tab, d_starts, split.fine, d_counter);
+        else spmm_batched_kernel<false, false><<<grid, block, 0, st>>>(d_tab, d_starts, split.fine, d_counter);
+    }
+    if (split.coarse > 0 && split.tiles_coarse > 0) {
+        dim3 grid((unsigned)std::min<long long>(split.tiles_coarse, (long long)ctx->sm_count * 8));
+        const BatchProblem *tab = d_tab + split.fine;
+        const long long *starts = d_starts + split.fine + 1;
+        if (ctx->strict_fp32) spmm_batched_kernel<true, true><<<grid, block, 0, st>>>(tab, starts, split.coarse, d_counter + 1);
+        else spmm_batched_kernel<false, true><<<grid, block, 0, st>>>(tab, starts, split.coarse, d_counter + 1);
+    }
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
@@ -304,7 +383,8 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     if (rc) return rc;
     std::vector<BatchProblem> tab;
     std::vector<long long> starts;
-    rc = build_tables(count, problems, tab, starts);  // validates; all problems, most work first
+    GatherSplit all_split;
+    rc = build_tables(ctx, count, problems, tab, starts, all_split);  // validates; all problems, most work first
     if (rc) return rc;
     dlspm_batch *b = new (std::nothrow) dlspm_batch();
     if (!b) return DLSPM_ERR_NOMEM;
@@ -318,7 +398,7 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     BatchProblem *d_all = nullptr;
     std::vector<int> flags(n, 0);
     cudaError_t err = cudaMalloc(&b->row_order_pool, sizeof(int) * std::max<size_t>(rows_total, 1));
-    if (err == cudaSuccess) err = cudaMalloc(&b->counters, 2 * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMalloc(&b->counters, 4 * sizeof(unsigned long long));
     if (err == cudaSuccess) err = cudaMalloc(&b->error, sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(b->error, 0, sizeof(int));
     if (err == cudaSuccess && n) {
@@ -348,7 +428,7 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     std::vector<long long> gstarts;
     std::vector<TileProblem> ttab;
     std::vector<long long> tstarts;
-    long long grun = 0, trun = 0;
+    long long trun = 0;
     for (size_t i = 0; i < n; i++) {
         const BatchProblem &t = tab[i];
         dlspm_problem q;
@@ -369,12 +449,10 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
             tp.pad = 0;
             ttab.push_back(tp);
         } else {
-            gstarts.push_back(grun);
-            grun += (long long)t.row_groups * dlspm_ceil_div(t.N, 32 * t.vec * t.chunks);
             gtab.push_back(t);
         }
     }
-    gstarts.push_back(grun);
+    finish_gather_tables(gtab, gstarts, b->split);
     // A tile of the tiled kernel costs ceil(K / 32) equal steps: with the problems in order of
     // decreasing K the fixed deal of tiles to thread blocks (block b takes tiles b, b + blocks, ...)
     // hands every block the same mix, the longest tiles first.
@@ -385,7 +463,6 @@ extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem
     }
     tstarts.push_back(trun);
     b->count = (int)gtab.size();
-    b->tiles = grun;
     b->tcount = (int)ttab.size();
     b->ttiles = trun;
     err = cudaMalloc(&b->problems, sizeof(BatchProblem) * std::max<size_t>(gtab.size(), 1));
@@ -418,8 +495,7 @@ extern "C" int dlspm_batch_launch_part(dlspm_ctx *ctx, const dlspm_batch *batch,
         if (rc) return rc;
     }
     if (part != 2) {
-        rc = batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counters, batch->count,
-                                 batch->tiles, st);
+        rc = batch_launch_tables(ctx, batch->problems, batch->tile_start, batch->counters, batch->split, st);
     }
     return rc;
 }
@@ -466,7 +542,7 @@ extern "C" int dlspm_batch_destroy(dlspm_batch *b)
 size_t dlspm_batched_table_bytes(int count)
 {
     const size_t tab = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
-    const size_t st = (sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255;
+    const size_t st = (sizeof(long long) * ((size_t)count + 2) + 255) & ~(size_t)255;
     return tab + st + 256;
 }
 
@@ -477,13 +553,14 @@ int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *proble
 {
     std::vector<BatchProblem> tab;
     std::vector<long long> starts;
-    int rc = build_tables(count, problems, tab, starts);
+    GatherSplit split;
+    int rc = build_tables(ctx, count, problems, tab, starts, split);
     if (rc) return rc;
     if (tab.empty()) return DLSPM_OK;
     const size_t tab_bytes = sizeof(BatchProblem) * tab.size();
     const size_t st_off = (sizeof(BatchProblem) * (size_t)count + 255) & ~(size_t)255;
     const size_t st_bytes = sizeof(long long) * starts.size();
-    const size_t cnt_off = st_off + ((sizeof(long long) * ((size_t)count + 1) + 255) & ~(size_t)255);
+    const size_t cnt_off = st_off + ((sizeof(long long) * ((size_t)count + 2) + 255) & ~(size_t)255);
     char *base = (char *)tables;
     const void *src_tab = tab.data(), *src_starts = starts.data();
     if (pinned) {
@@ -495,7 +572,7 @@ int dlspm_spmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_problem *proble
     DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, src_tab, tab_bytes, cudaMemcpyHostToDevice, st));
     DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base + st_off, src_starts, st_bytes, cudaMemcpyHostToDevice, st));
     return batch_launch_tables(ctx, (const BatchProblem *)base, (const long long *)(base + st_off),
-                               (unsigned long long *)(base + cnt_off), (int)tab.size(), starts.back(), st);
+                               (unsigned long long *)(base + cnt_off), split, st);
 }
 
 // One-shot grouped launch: tables go to the context's scratch (no allocation once it is large
@@ -615,7 +692,7 @@ extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dl
     for (int s0 = 0; s0 < used; s0 += kStaticChunk) {
         const int n = std::min(kStaticChunk, used - s0);
         for (int s = 0; s < n; s++) {
-            tab[s] = make_batch_problem(problems[order[s0 + s]]);
+            tab[s] = make_batch_problem(problems[order[s0 + s]], false);
             starts[s] = run;
             run += (long long)tab[s].row_groups * dlspm_ceil_div(tab[s].N, 32 * tab[s].vec * tab[s].chunks);
         }
@@ -625,5 +702,5 @@ extern "C" int dlspm_spmm_batched_f32_static(dlspm_ctx *ctx, int count, const dl
         DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(d_starts + s0, starts, sizeof(long long) * (size_t)(n + (last ? 1 : 0)),
                                             cudaMemcpyHostToDevice, st));
     }
-    return batch_launch_tables(ctx, d_tab, d_starts, d_counter, used, run, st);
+    return batch_launch_tables(ctx, d_tab, d_starts, d_counter, GatherSplit{used, 0, run, 0}, st);
 }

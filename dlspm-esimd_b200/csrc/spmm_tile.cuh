@@ -35,7 +35,19 @@
 namespace dlspm {
 
 constexpr int kTileN = 256, kTileK = 32;
-constexpr int kTileConsumers = 16;               // consumer warps per block
+#ifndef DLSPM_TILE_CONSUMERS
+#define DLSPM_TILE_CONSUMERS 16
+#endif
+constexpr int kTileConsumers = DLSPM_TILE_CONSUMERS;  // consumer warps per block (a multiple of four)
+// Registers per thread: at launch (what a block of this size may have), for the producer's group
+// after it has given registers up, and for the consumers after they have taken them.
+constexpr int kTileRegsLaunch = kTileConsumers == 16 ? 96 : 128;
+constexpr int kTileRegsProducer = kTileConsumers == 16 ? 32 : 40;
+constexpr int kTileRegsConsumer = kTileConsumers == 16 ? 112 : 152;
+static_assert(kTileConsumers == 16 || kTileConsumers == 12, "register budgets are set for 12 or 16 consumer warps");
+static_assert((kTileConsumers + 4) * 32 * kTileRegsLaunch <= 65536 &&
+                  kTileConsumers * 32 * kTileRegsConsumer + 128 * kTileRegsProducer <= (kTileConsumers + 4) * 32 * kTileRegsLaunch,
+              "register budgets exceed what the block is launched with");
 constexpr int kTileRowsPerWarp = 8;
 constexpr int kTileM = kTileConsumers * kTileRowsPerWarp;  // 128 rows of C per tile
 constexpr int kTileStages = 4;                   // B chunks in flight
@@ -302,33 +314,39 @@ struct TileRows {
     int end;     // end of the row in the CSR arrays
 };
 
-__device__ __forceinline__ void tile_rows_setup(TileRows &rs, const TileProblem &p, int rb, int warp, int lane)
+__device__ __forceinline__ void tile_rows_setup(TileRows &rs, const TileProblem *__restrict__ pp, int rb, int warp, int lane)
 {
     rs.row = -1;
     rs.cursor = 0;
     rs.end = 0;
     if (lane < kTileRowsPerWarp) {
         const int slot = rb * kTileM + warp * kTileRowsPerWarp + lane;
-        if (slot < p.M) {
-            rs.row = p.row_order ? __ldg(p.row_order + slot) : slot;
-            rs.cursor = __ldg(p.row_offsets + rs.row);
-            rs.end = __ldg(p.row_offsets + rs.row + 1);
+        if (slot < pp->M) {
+            const int *order = pp->row_order;
+            const int *offsets = pp->row_offsets;
+            rs.row = order ? __ldg(order + slot) : slot;
+            rs.cursor = __ldg(offsets + rs.row);
+            rs.end = __ldg(offsets + rs.row + 1);
         }
     }
 }
 
 // Starts the asynchronous fetch of the next <= 32 entries of this warp's rows; slots past the end of
 // a row get a column that no chunk contains.
-__device__ __forceinline__ void tile_fetch_candidates(TileSmem &sm, const TileProblem &p, const TileRows &rs, int warp,
-                                                      int lane)
+__device__ __forceinline__ void tile_fetch_candidates(TileSmem &sm, const TileProblem *__restrict__ pp, const TileRows &rs,
+                                                      int warp, int lane)
 {
+    // the two array bases are re-read from the problem table (an L1 hit) rather than kept in
+    // registers through the multiply loop
+    const int *cols = pp->cols;
+    const float *values = pp->values;
 #pragma unroll
     for (int r = 0; r < kTileRowsPerWarp; r++) {
         const int q = __shfl_sync(0xffffffffu, rs.cursor, r) + lane;
         const int e = __shfl_sync(0xffffffffu, rs.end, r);
         if (q < e) {
-            cp_async_4(&sm.cand_col[warp][r][lane], p.cols + q);
-            cp_async_4(&sm.cand_val[warp][r][lane], p.values + q);
+            cp_async_4(&sm.cand_col[warp][r][lane], cols + q);
+            cp_async_4(&sm.cand_val[warp][r][lane], values + q);
         } else {
             sm.cand_col[warp][r][lane] = 0x7fffffff;
         }
@@ -425,6 +443,27 @@ __device__ __forceinline__ void tile_chunk_masked(const TileSmem &sm, int s, int
     }
 }
 
+// The consumers' view of a tile: where it is, without a copy of the problem record.
+__device__ __forceinline__ bool tile_cursor_locate(TileCursor &tc, const TileProblem *__restrict__ problems,
+                                                   const long long *__restrict__ tile_start, int count, long long total)
+{
+    if (tc.tile >= total) return false;
+    int lo = tc.prob, hi = count - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(tile_start + mid) <= tc.tile) lo = mid;
+        else hi = mid - 1;
+    }
+    tc.prob = lo;
+    const int t = (int)(tc.tile - __ldg(tile_start + lo));
+    const int row_blocks = problems[lo].row_blocks;
+    const int cb = t / row_blocks;
+    tc.rb = t - cb * row_blocks;
+    tc.n0 = cb * kTileN;
+    tc.nchunks = (problems[lo].K + kTileK - 1) / kTileK;
+    return true;
+}
+
 template <bool STRICT>
 __device__ __forceinline__ bool tile_consumer(TileSmem &sm, const TileProblem *__restrict__ problems,
                                               const long long *__restrict__ tile_start, int count, long long total,
@@ -432,27 +471,27 @@ __device__ __forceinline__ bool tile_consumer(TileSmem &sm, const TileProblem *_
 {
     volatile int *abort = &sm.abort;
     TileCursor tc{(long long)blockIdx.x, 0, 0, 0, 0};
-    TileProblem p;
     unsigned g = 0;  // chunks consumed so far (the same numbering as the producer's)
-    while (tile_cursor_load(tc, problems, tile_start, count, total, p)) {
+    while (tile_cursor_locate(tc, problems, tile_start, count, total)) {
+        const TileProblem *pp = problems + tc.prob;
         TileRows rs;
-        tile_rows_setup(rs, p, tc.rb, warp, lane);
+        tile_rows_setup(rs, pp, tc.rb, warp, lane);
         // a warp whose 8 row slots all lie past the last row only keeps the barriers moving
-        const bool idle = tc.rb * kTileM + warp * kTileRowsPerWarp >= p.M;
+        const bool idle = tc.rb * kTileM + warp * kTileRowsPerWarp >= pp->M;
         float2 acc[kTileRowsPerWarp][4];
 #pragma unroll
         for (int i = 0; i < kTileRowsPerWarp; i++)
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[i][j] = make_float2(0.f, 0.f);
         if (!idle) {
-            tile_fetch_candidates(sm, p, rs, warp, lane);
+            tile_fetch_candidates(sm, pp, rs, warp, lane);
             tile_expand_a(sm, rs, (int)(g & 1u), 0, warp, lane);
         }
         for (int c = 0; c < tc.nchunks; c++, g++) {
             const int s = (int)(g % kTileStages);
             const int buf = (int)(g & 1u);
             const bool more = c + 1 < tc.nchunks;
-            if (more && !idle) tile_fetch_candidates(sm, p, rs, warp, lane);  // lands while this chunk is computed
+            if (more && !idle) tile_fetch_candidates(sm, pp, rs, warp, lane);  // lands while this chunk is computed
             if (!mbar_wait_or_abort(&sm.ready[s], (g / kTileStages) & 1u, abort)) return false;
             if (!idle) {
                 if (force_masked || sm.nonfinite[s]) tile_chunk_masked<STRICT>(sm, s, warp, buf, lane, acc);
@@ -463,14 +502,16 @@ __device__ __forceinline__ bool tile_consumer(TileSmem &sm, const TileProblem *_
             if (lane == 0) mbar_arrive(&sm.empty[s]);  // this warp is done with the stage
         }
         if (!idle) {
+            float *cbase = pp->C;
+            const int ncols = pp->N;
 #pragma unroll
             for (int i = 0; i < kTileRowsPerWarp; i++) {
                 const int row = __shfl_sync(0xffffffffu, rs.row, i);
                 if (row >= 0) {
-                    float *crow = p.C + (size_t)row * (size_t)p.N + tc.n0;
-                    if (tc.n0 + lane * 4 < p.N)
+                    float *crow = cbase + (size_t)row * (size_t)ncols + tc.n0;
+                    if (tc.n0 + lane * 4 < ncols)
                         *reinterpret_cast<float4 *>(crow + lane * 4) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
-                    if (tc.n0 + 128 + lane * 4 < p.N)
+                    if (tc.n0 + 128 + lane * 4 < ncols)
                         *reinterpret_cast<float4 *>(crow + 128 + lane * 4) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
                 }
             }
@@ -505,15 +546,14 @@ spmm_tile_kernel(const TileProblem *__restrict__ problems, const long long *__re
     }
     __syncthreads();
     const long long total = tile_start[count];
-    // Registers move from the producer's group of four warps to the consumers (the block is launched
-    // with 96 per thread): the producer's loop needs few, the consumers hold 64 accumulators each.
+    // Registers move from the producer's group of four warps to the consumers (see kTileRegsLaunch): the producer's loop needs few, the consumers hold 64 accumulators each.
     bool ok = true;
     if (warp >= kTileConsumers) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTileRegsProducer));
         // the producer and the three spare warps of its group, which leave at once
         if (warp == kTileConsumers) ok = tile_producer(sm, problems, tile_start, count, total, lane);
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTileRegsConsumer));
         ok = tile_consumer<STRICT>(sm, problems, tile_start, count, total, force_masked != 0, warp, lane);
     }
     if (!ok) {
