@@ -1,4 +1,5 @@
 // cuSPARSE beside this library on the same inputs: ./cusparse-compare spmm|sddmm <M> <K> <N> <density>
+// or, for the 72 cases of the reference's comparison grid in one process: ./cusparse-compare spmm|sddmm grid
 // Comparison only, as in the reference (CUSPARSE/spmm.cu, CUSPARSE/sddmm.cu): cusparseSpMM and
 // cusparseSDDMM with ALG_DEFAULT on row-major fp32 operands, minimum of 20 event-timed runs, next
 // to dlspm_spmm_csr_f32 / dlspm_sddmm_csr_f32 timed the same way, plus the largest difference
@@ -16,19 +17,9 @@
         }                                                                        \
     } while (0)
 
-int main(int argc, char **argv)
+// One comparison: the same CSR pattern and dense operands through cuSPARSE and through this library.
+static int compare_case(dlspm_ctx *ctx, const drv::Options &o, bool spmm, int M, int K, int N, double density)
 {
-    drv::Options o = drv::parse(argc, argv);
-    if (o.positional.size() != 5 || (o.positional[0] != "spmm" && o.positional[0] != "sddmm")) {
-        printf("Usage: ./cusparse-compare spmm|sddmm <M> <K> <N> <density>\n");
-        return 0;
-    }
-    const bool spmm = o.positional[0] == "spmm";
-    const int M = atoi(o.positional[1].c_str()), K = atoi(o.positional[2].c_str()), N = atoi(o.positional[3].c_str());
-    const double density = atof(o.positional[4].c_str());
-    dlspm_ctx *ctx = nullptr;
-    DRV_TRY(dlspm_create(&ctx, o.device));
-    drv::print_device(ctx);
     std::vector<int> ro, ci;
     DRV_TRY(drv::make_bernoulli(M, K, density, o.seed, ro, ci));
     const int nnz = (int)ci.size();
@@ -104,6 +95,38 @@ int main(int argc, char **argv)
     cusparseDestroyDnMat(matM);
     cusparseDestroy(handle);
     cudaFree(d_buffer);
-    dlspm_destroy(ctx);
+    cudaFree(d_ro); cudaFree(d_ci); cudaFree(d_vals); cudaFree(d_k); cudaFree(d_m); cudaFree(d_ours); cudaFree(d_theirs);
     return 0;
+}
+
+int main(int argc, char **argv)
+{
+    drv::Options o = drv::parse(argc, argv);
+    const bool grid = o.positional.size() == 2 && o.positional[1] == "grid";
+    if ((o.positional.size() != 5 && !grid) || (o.positional[0] != "spmm" && o.positional[0] != "sddmm")) {
+        printf("Usage: ./cusparse-compare spmm|sddmm <M> <K> <N> <density>\n       ./cusparse-compare spmm|sddmm grid\n");
+        return 0;
+    }
+    const bool spmm = o.positional[0] == "spmm";
+    dlspm_ctx *ctx = nullptr;
+    DRV_TRY(dlspm_create(&ctx, o.device));
+    drv::print_device(ctx);
+    int rc = 0;
+    if (grid) {
+        // the reference's comparison grid (CUSPARSE/batch-spmm:8-24, the shapes of
+        // SPMM/spmm-esimd-allbenchs2.cpp:259-262): 12 (M, K) pairs x density {0.3, 0.2, 0.1} x N {32, 128}
+        const int MSZ_arr[12] = {1024, 3072, 4096, 2048, 6144, 8192, 4096, 12288, 16384, 8192, 24576, 32768};
+        const int KSZ_arr[12] = {1024, 1024, 1024, 2048, 2048, 2048, 4096, 4096, 4096, 8192, 8192, 8192};
+        const int NSZ_arr[2] = {32, 128};
+        const double SP_arr[3] = {0.3, 0.2, 0.1};
+        for (int N : NSZ_arr)
+            for (int c = 0; c < 12 && rc == 0; c++)
+                for (double sp : SP_arr)
+                    if ((rc = compare_case(ctx, o, spmm, MSZ_arr[c], KSZ_arr[c], N, sp)) != 0) break;
+    } else {
+        rc = compare_case(ctx, o, spmm, atoi(o.positional[1].c_str()), atoi(o.positional[2].c_str()),
+                          atoi(o.positional[3].c_str()), atof(o.positional[4].c_str()));
+    }
+    dlspm_destroy(ctx);
+    return rc;
 }

@@ -309,8 +309,10 @@ struct ScatterArgs {
 };
 
 template <int VEC, int U, bool STRICT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(const ScatterArgs s)
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_rows_scatter_kernel(const __grid_constant__ ScatterArgs s)
 {
+    // (__grid_constant__: the destination list is indexed with a run-time index below; without it
+    // every thread would first copy the argument block to local memory)
     __shared__ int2 stage[kWarpsPerCta][32];
     const SpmmArgs &a = s.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

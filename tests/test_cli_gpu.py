@@ -106,3 +106,40 @@ def test_sweep_drivers_single_case(pkg):
     assert "GFLOPS:" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
     out = _run(pkg, "sddmm-allbench", 1024, 1024, 32, 0.1)
     assert "GFLOPS :" in out and _value(out, r"max_diff = ([0-9.e+-]+)") < 1e-4
+
+
+def test_batch_scripts_walk_a_tree_in_one_process(pkg, tmp_path):
+    """batch-run-*_fromfile over a small DLMC-style tree: one driver process runs every file of the
+    tree (--list), widths come from the "<name>,<N>" table, the host check covers a sample of the
+    rows (--check-rows), and the CSV has one row per file."""
+    tree = tmp_path / "dlmc" / "rn50" / "magnitude_pruning"
+    names = ["layer_a", "layer_b", "layer_c"]
+    for sp in ("0.5", "0.9"):
+        (tree / sp).mkdir(parents=True)
+        for i, n in enumerate(names):
+            ro, ci = pkg.gen_bernoulli_csr_host(128 + 64 * i, 96, 1.0 - float(sp), 20 + i)
+            pkg.write_smtx(str(tree / sp / f"{n}.smtx"), 128 + 64 * i, 96, ro, ci)
+    table = tmp_path / "widths.txt"
+    table.write_text("layer_a,64\nlayer_b,49\nlayer_c,256\n")
+    for op, cols in (("spmm", 7), ("sddmm", 7)):
+        script = os.path.join(pkg.PKG_DIR, "cli", f"batch-run-{op}_fromfile")
+        p = subprocess.run(["bash", script, str(tmp_path / "dlmc" / "rn50"), str(table), "--check-rows", "16"],
+                           cwd=tmp_path, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+        assert p.returncode == 0, p.stdout
+        csvs = [f for f in os.listdir(tmp_path) if f.startswith(f"{op}-fromfile_") and f.endswith(".csv")]
+        reports = [f for f in os.listdir(tmp_path) if f.startswith(f"summary-perf-{op}-")]
+        assert len(csvs) == 1 and len(reports) == 1
+        rows = [r.split(",") for r in open(tmp_path / csvs[0]).read().strip().splitlines()]
+        assert len(rows) == 6 and all(len(r) == cols for r in rows)
+        text = open(tmp_path / reports[0]).read()
+        assert text.count("Filename = ") == 6 and "host check on every" in text
+        for m in re.finditer(r"max_diff = ([0-9.e+-]+)", text):
+            assert float(m.group(1)) < 1e-3
+    # a table with the single line "*,<N>" gives every file that width
+    table.write_text("*,32\n")
+    script = os.path.join(pkg.PKG_DIR, "cli", "batch-run-spmm_fromfile")
+    p = subprocess.run(["bash", script, str(tmp_path / "dlmc" / "rn50"), str(table), "--no-check"], cwd=tmp_path,
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout
+    report = [f for f in os.listdir(tmp_path) if f.startswith("summary-perf-spmm-")][0]
+    assert open(tmp_path / report).read().count("NSZ: 32") == 6

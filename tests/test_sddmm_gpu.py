@@ -201,3 +201,4 @@ def test_tiny_patterns_share_rows_and_passes(pkg, oracle, ctx, dev, M, K, N, den
     lhs = dense(pkg, M, N, 1000 + M, 11, kind=pkg.KIND_NORMAL)
     rhs = dense(pkg, K, N, 1000 + M, 12, kind=pkg.KIND_NORMAL)
     check(oracle, ro, ci, lhs, rhs, M, N, run_sddmm(ctx, dev, M, K, N, ro, ci, lhs, rhs))
+
