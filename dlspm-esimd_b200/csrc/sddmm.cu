@@ -138,10 +138,43 @@ sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
     }
 }
 
+// Patterns of one to a few waves of thread blocks: the last wave is often nearly empty (6144 rows are
+// 768 blocks for 592 resident ones, i.e. two waves for 1.3 waves of work).  Two or four warps per
+// row make the blocks shorter and the waves finer; a shared row costs about 8 % per doubling (every
+// warp loads the lhs row, shorter runs per warp).  Returns the shift with the least estimated time.
+inline int sddmm_wave_shift(long long blocks, long long resident, double avg_row)
+{
+    if (blocks <= resident || blocks > 8 * resident) return 0;
+    int best = 0;
+    double best_cost = 1e30;
+    for (int s = 0; s <= 2 && avg_row > 32.0 * (1 << s); s++) {
+        const long long waves = ((blocks << s) + resident - 1) / resident;
+        const double cost = (double)waves / (double)(1 << s) * (1.0 + 0.08 * s);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = s;
+        }
+    }
+    return best;
+}
+
 template <int G, int R>
 void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M,
-                 int chunks, const float *mask, int split_shift, int k_shift, int sm_count, cudaStream_t st)
+                 int chunks, const float *mask, int split_shift, int k_shift, int sm_count, cudaStream_t st,
+                 double avg_row = 0.0)
 {
+    if (split_shift == 0 && k_shift == 0 && avg_row > 0.0) {
+        static int per_sm = 0;  // resident blocks of the plain build of this layout
+        if (per_sm == 0) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sddmm_rows_kernel<G, R, false>, kWarps * 32, 0) != cudaSuccess) {
+                (void)cudaGetLastError();
+                n = 4;
+            }
+            per_sm = n > 0 ? n : 4;
+        }
+        split_shift = sddmm_wave_shift(((long long)M + kWarps - 1) / kWarps, (long long)per_sm * sm_count, avg_row);
+    }
     const long long warps = (long long)M << (split_shift + k_shift);
     const unsigned blocks = (unsigned)((warps + kWarps - 1) / kWarps);
     if constexpr (G == 8 && R == 2) {
@@ -216,12 +249,12 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         const int chunks = N / 4;
         const int shift = sddmm_split_shift(ctx, M, nnz);
         const int kshift = sddmm_k_shift(ctx, M, nnz, shift, 16.0);
-        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
-        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
-        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st);
+        if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 16) launch_fast<16, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 32 && R == 4) launch_fast<32, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
+        else launch_fast<32, 8>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
     } else if (vec == 4) {
         // measured: 512-float segments (80 registers, 3 blocks per SM) win from N = 3136, 1024-float
         // segments below that
