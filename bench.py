@@ -39,10 +39,12 @@ WIDTHS = [256, 1024, 3136]
 COV = 0.4
 STREAM_PICK = 50
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per algorithmic byte of spmm_batched_kernel, from one ncu capture of a 256-problem
-# batch (dram__bytes_read.sum + dram__bytes_write.sum = 4.39 GB for 3.87 GB algorithmic).  Traffic
-# grows with the bytes of the problems processed, so the ratio is applied to the full launch.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"spmm_batched_kernel": 1.134}
+# DRAM bytes per algorithmic byte of the two kernels of a step, from one ncu capture each on the
+# first 256 problems of the batch (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic
+# bytes of the problems the kernel served: 2.18 + 0.61 GB for 3.06 GB on the row-gather kernel, whose
+# last results are still in L2 when it ends; 0.72 + 0.16 GB for 0.82 GB on the tiled kernel).  Traffic
+# grows with the bytes of the problems processed, so the ratios are applied to the full launch.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"spmm_batched_kernel": 0.913, "spmm_tile_kernel": 1.077}
 
 
 def log(*a):

@@ -20,8 +20,8 @@ using namespace dlspm;
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kClasses = 6;  // (G, R) layouts of sddmm_layout
-constexpr int kOpSddmm = 0, kOpFused = 1;
+constexpr int kClasses = 8;  // the six (G, R) layouts of sddmm_layout, then SDDMM rows beyond 1024 floats in segments of 1024 / 512
+constexpr int kOpSddmm = 0, kOpFused = 1, kOpSddmmLong = 2;
 
 struct RowProblem {
     const int *row_offsets;
@@ -52,6 +52,35 @@ __device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int 
         col_next = q + 32 < end ? __ldg(p.cols + q + 32) : -1;
         const float r = sddmm_pass<G, R>(a, rhs4, p.chunks, col, g, t);
         if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * r : r;
+    }
+}
+
+// Inner dimension beyond 1024: the partial dot products of a pass are accumulated over segments of
+// 32*R float4 of the two rows and reduced once per pass, as in the single-matrix kernel for long rows.
+template <int R>
+__device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row, int lane)
+{
+    constexpr int G = 32, kSeg = G * R;
+    const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+    if (start >= end) return;
+    const float4 *lhs4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
+    const float4 *rhs4 = reinterpret_cast<const float4 *>(p.b);
+    int col_next = start + lane < end ? __ldg(p.cols + start + lane) : -1;
+    for (int base = start; base < end; base += 32) {
+        const int q = base + lane;
+        const int col = col_next;
+        col_next = q + 32 < end ? __ldg(p.cols + q + 32) : -1;
+        float part[G];
+#pragma unroll
+        for (int k = 0; k < G; k++) part[k] = 0.f;
+        for (int seg = 0; seg < p.chunks; seg += kSeg) {
+            const int len = min(kSeg, p.chunks - seg);
+            float4 a[R];
+            load_row_chunks<G, R>(lhs4 + seg, len, lane, a);
+            sddmm_accumulate<G, R, false>(part, a, rhs4 + seg, len, p.chunks, col, 0, lane);
+        }
+        group_transpose_reduce<G>(part, lane);
+        if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * part[0] : part[0];
     }
 }
 
@@ -104,7 +133,8 @@ rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__
         const RowProblem p = problems[lo];
         const int row = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
         if (row < p.M) {
-            if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, lane);
+            if constexpr (OP == kOpSddmmLong) sddmm_one_row_long<R>(p, row, lane);
+            else if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, lane);
             else fused_one_row<G, R>(p, row, lane);
         }
     }
@@ -139,7 +169,9 @@ int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, cons
     case 2: return launch_class<8, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     case 3: return launch_class<16, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     case 4: return launch_class<32, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    default: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 5: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 6: return launch_class<32, 8, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    default: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     }
 }
 
@@ -253,12 +285,16 @@ int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem 
         const dlspm_sddmm_problem &q = problems[i];
         if (q.M == 0 || q.nnz == 0) continue;
         int G = 0, R = 0;
-        if (q.N > 0 && dlspm_vec_width(q.N, q.lhs, q.rhs) == 4 && sddmm_layout(q.N / 4, &G, &R)) {
+        const bool wide = q.N > 0 && dlspm_vec_width(q.N, q.lhs, q.rhs) == 4;
+        if (wide) {
             HostEntry e;
             e.p = RowProblem{q.row_offsets, q.column_indices, q.lhs, q.rhs, nullptr, q.mask_values, q.out_values, q.M, q.N / 4};
             e.work = (double)q.nnz * q.N;
             e.index = i;
-            by_class[layout_class(G, R)].push_back(e);
+            // beyond the register-resident layouts: segments of 1024 floats, of 512 from N = 2052 on
+            // (the choice of the single-matrix launcher)
+            const int cls = sddmm_layout(q.N / 4, &G, &R) ? layout_class(G, R) : (q.N > 2048 ? 7 : 6);
+            by_class[cls].push_back(e);
         } else {
             int rc = dlspm_sddmm_csr_masked_f32(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices, q.mask_values,
                                                 q.lhs, q.rhs, q.out_values, st);

@@ -212,13 +212,13 @@ typedef struct dlspm_fused_problem {
 } dlspm_fused_problem;
 
 /* Runs `count` independent SDDMMs (each as dlspm_sddmm_csr_masked_f32 would) in one persistent
- * launch per register layout present in the batch (the layout follows from N: at most six, one for
+ * launch per register layout present in the batch (the layout follows from N: at most eight, one for
  * a batch with a single inner dimension).  Replaces the per-matrix process launches of
  * SDDMM/batch-run-sddmm_fromfile:31-47, where every layer-sized pattern is launch-bound on its own.
  * `problems` is a HOST array; the tables go to the context's scratch, so the same rules as for
  * dlspm_spmm_batched_f32 hold: calls on one context ordered on one stream, not on a capturing
- * stream.  Problems whose N or pointers rule out 128-bit loads, or with N > 1024, are run one by
- * one with the single-matrix kernels inside the same call. */
+ * stream.  Problems whose N or pointers rule out 128-bit loads (for the fused chain also those with
+ * N > 1024) are run one by one with the single-matrix kernels inside the same call. */
 int dlspm_sddmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem *problems, void *stream);
 /* The same for the fused SDDMM -> SpMM chain (each problem as dlspm_fused_sddmm_spmm_f32 would);
  * replaces the per-matrix runs of FUSED/batch-run-fused:22-34. */
