@@ -45,7 +45,12 @@ __device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, in
         spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
 }
 
-constexpr int kCoarseRows = 8 * kWarpsPerCta;  // rows per tile of the coarse launch
+// Warps (= rows of a fine tile) per thread block of the grouped launch.
+#ifndef DLSPM_BATCH_WARPS
+#define DLSPM_BATCH_WARPS 8
+#endif
+constexpr int kBatchWarps = DLSPM_BATCH_WARPS;
+constexpr int kCoarseRows = 64 > 2 * kBatchWarps ? 64 : 2 * kBatchWarps;  // rows per tile of the coarse launch
 
 template <bool STRICT>
 __device__ __forceinline__ void batched_row(const BatchProblem &p, int slab, int slot, int lane, int2 *stage)
@@ -63,11 +68,11 @@ __device__ __forceinline__ void batched_row(const BatchProblem &p, int slab, int
 // COARSE: the tiles of this launch cover 64 rows (each warp walks eight of them) instead of 8; a
 // build of its own, because the extra loop costs the common build registers it does not have.
 template <bool STRICT, bool COARSE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kBatchWarps * 32)
 spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *__restrict__ tile_start,
                     int count, unsigned long long *counter)
 {
-    __shared__ int2 stage[kWarpsPerCta][32];
+    __shared__ int2 stage[kBatchWarps][32];
     __shared__ unsigned long long s_tile;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total = tile_start[count];
@@ -90,9 +95,9 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
             const int first = (int)(t - (long long)slab * p.row_groups) * kCoarseRows;
             const int last = min(first + kCoarseRows, p.M);
 #pragma unroll 1
-            for (int slot = first + warp; slot < last; slot += kWarpsPerCta) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
+            for (int slot = first + warp; slot < last; slot += kBatchWarps) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
         } else {
-            const int slot = (int)(t - (long long)slab * p.row_groups) * kWarpsPerCta + warp;
+            const int slot = (int)(t - (long long)slab * p.row_groups) * kBatchWarps + warp;
             if (slot < p.M) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
         }
     }
@@ -109,8 +114,8 @@ namespace {
 // and finer tiles balance better).
 inline int rows_per_tile_for(const dlspm_problem &q, bool allow_coarse)
 {
-    if (!allow_coarse || q.M <= kWarpsPerCta) return kWarpsPerCta;
-    return (double)q.nnz <= 32.0 * (double)q.M ? kCoarseRows : kWarpsPerCta;
+    if (!allow_coarse || q.M <= kBatchWarps) return kBatchWarps;
+    return (double)q.nnz <= 32.0 * (double)q.M ? kCoarseRows : kBatchWarps;
 }
 
 // (One-chunk slabs for such problems, so that the slab of B would stay in L1 for the 64 rows of a
@@ -184,10 +189,10 @@ struct GatherSplit {
 // Orders a table (already sorted by decreasing work) fine problems first and builds its tile index.
 void finish_gather_tables(std::vector<BatchProblem> &tab, std::vector<long long> &starts, GatherSplit &split)
 {
-    std::stable_partition(tab.begin(), tab.end(), [](const BatchProblem &b) { return b.rows_per_tile == kWarpsPerCta; });
+    std::stable_partition(tab.begin(), tab.end(), [](const BatchProblem &b) { return b.rows_per_tile == kBatchWarps; });
     starts.clear();
     split = GatherSplit{0, 0, 0, 0};
-    for (const BatchProblem &b : tab) split.fine += b.rows_per_tile == kWarpsPerCta ? 1 : 0;
+    for (const BatchProblem &b : tab) split.fine += b.rows_per_tile == kBatchWarps ? 1 : 0;
     split.coarse = (int)tab.size() - split.fine;
     long long run = 0;
     for (int i = 0; i < split.fine; i++) {
@@ -319,14 +324,14 @@ int batch_launch_tables(dlspm_ctx *ctx, const BatchProblem *d_tab, const long lo
 {
     if (split.tiles_fine == 0 && split.tiles_coarse == 0) return DLSPM_OK;
     DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counter, 0, 2 * sizeof(unsigned long long), st));
-    dim3 block(kWarpsPerCta * 32);
+    dim3 block(kBatchWarps * 32);
     if (split.fine > 0 && split.tiles_fine > 0) {
-        dim3 grid((unsigned)std::min<long long>(split.tiles_fine, (long long)ctx->sm_count * 8));
+        dim3 grid((unsigned)std::min<long long>(split.tiles_fine, (long long)ctx->sm_count * (64 / kBatchWarps)));
         if (ctx->strict_fp32) spmm_batched_kernel<true, false><<<grid, block, 0, st>>>(d_tab, d_starts, split.fine, d_counter);
         else spmm_batched_kernel<false, false><<<grid, block, 0, st>>>(d_tab, d_starts, split.fine, d_counter);
     }
     if (split.coarse > 0 && split.tiles_coarse > 0) {
-        dim3 grid((unsigned)std::min<long long>(split.tiles_coarse, (long long)ctx->sm_count * 8));
+        dim3 grid((unsigned)std::min<long long>(split.tiles_coarse, (long long)ctx->sm_count * (64 / kBatchWarps)));
         const BatchProblem *tab = d_tab + split.fine;
         const long long *starts = d_starts + split.fine + 1;
         if (ctx->strict_fp32) spmm_batched_kernel<true, true><<<grid, block, 0, st>>>(tab, starts, split.coarse, d_counter + 1);
