@@ -134,6 +134,7 @@ _SIGNATURES = {
     "dlspm_measure_fp32_peak": (_I, [_P, C.POINTER(C.c_double)]),
     "dlspm_measure_fp32_peaks": (_I, [_P, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "dlspm_host_copy_count": (_I, [_P, C.POINTER(C.c_longlong)]),
+    "dlspm_sanity_check_csr": (_I, [_P, _I, _I, _I, _P, _P, C.c_char_p, C.c_size_t, _P]),
     "dlspm_selftest_bounded_wait": (_I, [_P, C.c_uint, C.POINTER(_I)]),
     "dlspm_spmm_csr_f32_scatter": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _I, C.POINTER(_P), C.c_longlong, _P]),
     "dlspm_enable_peer_access": (_I, [_P, _I]),
@@ -397,6 +398,16 @@ class Context:
         a, b = C.c_double(), C.c_double()
         _check(self.lib.dlspm_measure_fp32_peaks(self.handle, C.byref(a), C.byref(b)), "dlspm_measure_fp32_peaks", self)
         return a.value, b.value
+
+    def sanity_check_csr(self, M, K, nnz, row_offsets, column_indices, stream=None):
+        """Device-side CSR validation: (status, reason)."""
+        import torch
+
+        why = C.create_string_buffer(256)
+        st = self.lib.dlspm_sanity_check_csr(self.handle, M, K, nnz, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
+                                             _dev_ptr(column_indices, torch.int32, "column_indices"), why, 256,
+                                             _stream_ptr(stream))
+        return st, why.value.decode()
 
     def host_copy_count(self) -> int:
         """cudaMemcpyAsync calls issued so far by spmm_batched_host on this context."""

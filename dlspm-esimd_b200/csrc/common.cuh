@@ -19,6 +19,7 @@ struct dlspm_ctx {
     int strict_fp32;  // DLSPM_OPT_STRICT_FP32
     int spmm_kernel;  // DLSPM_OPT_SPMM_KERNEL
     int tile_min_density_permille;  // DLSPM_OPT_TILE_MIN_DENSITY
+    int tile_min_density_set;       // the caller has set it (a forced kernel choice honours only an explicit threshold)
     // Device scratch owned by the context, grown on demand (grouped-launch tables, staging for
     // the host-buffer entry points).  Freed in dlspm_destroy.
     void *scratch;

@@ -31,6 +31,9 @@ extern "C" const char *dlspm_strerror(int status)
     }
 }
 
+// measured crossover: the tiled kernel wins from about 45 % nonzeros
+static constexpr int kDefaultTileMinDensity = 450;
+
 extern "C" int dlspm_create(dlspm_ctx **out, int device)
 {
     if (!out || device < 0) return DLSPM_ERR_INVALID_ARGUMENT;
@@ -45,7 +48,7 @@ extern "C" int dlspm_create(dlspm_ctx **out, int device)
     if (!ctx) return DLSPM_ERR_NOMEM;
     memset(ctx, 0, sizeof(*ctx));
     ctx->device = device;
-    ctx->tile_min_density_permille = 450;  // measured crossover: the tiled kernel wins from about 45 % nonzeros
+    ctx->tile_min_density_permille = kDefaultTileMinDensity;
     cudaDeviceProp prop;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -113,8 +116,14 @@ extern "C" int dlspm_set_option(dlspm_ctx *ctx, int option, int value)
         ctx->spmm_kernel = value;
         return DLSPM_OK;
     case DLSPM_OPT_TILE_MIN_DENSITY:
+        if (value == -1) {  // back to the default, as if never set
+            ctx->tile_min_density_permille = kDefaultTileMinDensity;
+            ctx->tile_min_density_set = 0;
+            return DLSPM_OK;
+        }
         if (value < 0 || value > 1001) return DLSPM_ERR_INVALID_ARGUMENT;
         ctx->tile_min_density_permille = value;
+        ctx->tile_min_density_set = 1;
         return DLSPM_OK;
     default: return DLSPM_ERR_INVALID_ARGUMENT;
     }
@@ -360,4 +369,79 @@ extern "C" int dlspm_selftest_bounded_wait(dlspm_ctx *ctx, unsigned polls, int *
     DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(timed_out, ctx->scratch, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     return *timed_out ? DLSPM_ERR_TIMEOUT : DLSPM_OK;
+}
+
+// ---- CSR validation on the device -------------------------------------------------------------------
+// The kernels trust the CSR arrays as the reference's do (a column index beyond K reads outside B).
+// For arrays that never were on the host this is the reference's SanityCheck
+// (SPMM/spmm-esimd-fromfile.cpp:36-61, plus row_offsets[0] == 0 and column >= 0) run on the device:
+// status[0] = kind of the first violation found (0 = none), status[1] = where.
+namespace {
+
+enum { kCsrOk = 0, kCsrFirstOffset = 1, kCsrLastOffset = 2, kCsrDecreasing = 3, kCsrRowTooLong = 4, kCsrColumn = 5 };
+
+__global__ void __launch_bounds__(256) csr_check_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                                                       int M, int K, int nnz, int *status)
+{
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    int kind = kCsrOk, where = 0;
+    if (tid == 0) {
+        if (row_offsets[0] != 0) { kind = kCsrFirstOffset; where = 0; }
+        else if (row_offsets[M] != nnz) { kind = kCsrLastOffset; where = M; }
+    }
+    for (long long i = tid; i < M && kind == kCsrOk; i += step) {
+        const int a = row_offsets[i], b = row_offsets[i + 1];
+        if (b < a) { kind = kCsrDecreasing; where = (int)i; }
+        else if (b - a > K) { kind = kCsrRowTooLong; where = (int)i; }
+    }
+    // columns are read only inside [0, nnz), whatever the offsets say
+    for (long long p = tid; p < nnz && kind == kCsrOk; p += step) {
+        const int c = cols[p];
+        if (c < 0 || c >= K) { kind = kCsrColumn; where = (int)p; }
+    }
+    if (kind != kCsrOk && atomicCAS(&status[0], 0, kind) == 0) status[1] = where;
+}
+
+}  // namespace
+
+extern "C" int dlspm_sanity_check_csr(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets,
+                                      const int *column_indices, char *why, size_t why_len, void *stream)
+{
+    if (!ctx || M < 0 || K < 0 || nnz < 0 || !row_offsets || (nnz > 0 && !column_indices)) return DLSPM_ERR_INVALID_ARGUMENT;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    if (why && why_len) why[0] = 0;
+    if ((long long)nnz > (long long)M * (long long)K) {
+        if (why && why_len) snprintf(why, why_len, "nnz is larger than matrix.");
+        return DLSPM_ERR_CSR;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int *status = nullptr;
+    DLSPM_CUDA_TRY(ctx, cudaMalloc(&status, 2 * sizeof(int)));
+    int host[2] = {0, 0};
+    cudaError_t err = cudaMemsetAsync(status, 0, 2 * sizeof(int), st);
+    if (err == cudaSuccess) {
+        const long long work = (long long)M > (long long)nnz ? M : nnz;
+        const int blocks = (int)((work + 255) / 256 < 1 ? 1 : ((work + 255) / 256 > (long long)ctx->sm_count * 16 ? (long long)ctx->sm_count * 16 : (work + 255) / 256));
+        csr_check_kernel<<<blocks, 256, 0, st>>>(row_offsets, column_indices, M, K, nnz, status);
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) err = cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    cudaFree(status);
+    if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "device CSR check");
+    if (host[0] == kCsrOk) return DLSPM_OK;
+    if (why && why_len) {
+        // the reference's exception texts where it has one
+        // the host check's texts (the reference's exception texts where it has one), plus the place
+        switch (host[0]) {
+        case kCsrFirstOffset: snprintf(why, why_len, "a_row_offsets[0] != 0"); break;
+        case kCsrLastOffset: snprintf(why, why_len, "a_row_offsets[MSZ] != nnz."); break;
+        case kCsrDecreasing: snprintf(why, why_len, "a_row_offsets[i+1] < a_row_offsets[i] (i = %d)", host[1]); break;
+        case kCsrRowTooLong: snprintf(why, why_len, "a_row_offsets[i + 1] - a_row_offsets[i] > KSZ (i = %d)", host[1]); break;
+        default: snprintf(why, why_len, "a_column_indices[i] >= KSZ or < 0 (i = %d)", host[1]); break;
+        }
+    }
+    return DLSPM_ERR_CSR;
 }

@@ -373,7 +373,8 @@ bool prefer_tiled(const dlspm_ctx *ctx, const dlspm_problem &q, int vec, bool so
     const double density = (double)q.nnz / ((double)q.M * (double)q.K);
     // choices 2 and 3 take every eligible problem unless a density threshold was set as well
     if (ctx->spmm_kernel >= 2)
-        return ctx->tile_min_density_permille > 1000 || density * 1000.0 >= (double)ctx->tile_min_density_permille;
+        return !ctx->tile_min_density_set || ctx->tile_min_density_permille > 1000 ||
+               density * 1000.0 >= (double)ctx->tile_min_density_permille;
     return density * 1000.0 >= (double)ctx->tile_min_density_permille && q.M >= 16 && q.N >= 64;
 }
 

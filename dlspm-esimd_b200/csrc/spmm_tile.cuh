@@ -35,14 +35,6 @@
 namespace dlspm {
 
 constexpr int kTileN = 256, kTileK = 32;
-#ifndef DLSPM_MASKED_UNROLL
-#define DLSPM_MASKED_UNROLL 1
-#endif
-#ifndef DLSPM_MASKED_SKIP
-#define DLSPM_MASKED_SKIP 1
-#endif
-constexpr int kMaskedUnroll = DLSPM_MASKED_UNROLL;
-constexpr bool kMaskedSkip = DLSPM_MASKED_SKIP != 0;
 #ifndef DLSPM_TILE_CONSUMERS
 #define DLSPM_TILE_CONSUMERS 16
 #endif
@@ -433,9 +425,9 @@ __device__ __forceinline__ void tile_chunk_masked(const TileSmem &sm, int s, int
         m[i] = sm.Am[warp][buf][i];
         any |= m[i];
     }
-#pragma unroll(kMaskedUnroll)
+#pragma unroll 1
     for (int k = 0; k < kTileK; k++) {
-        if (kMaskedSkip && !((any >> k) & 1u)) continue;  // none of this warp's rows uses the column
+        if (!((any >> k) & 1u)) continue;  // none of this warp's rows uses the column
         const float4 a0 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp);
         const float4 a1 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp + 4);
         const float4 b0 = *reinterpret_cast<const float4 *>(bs + k * kTileN);

@@ -69,17 +69,19 @@ typedef enum dlspm_option {
      * bit for bit.  0 (default): fused multiply-add. */
     DLSPM_OPT_STRICT_FP32 = 0,
     /* SpMM kernel choice in prepared batches: 0 = automatic (density threshold below), 1 = row-gather
-     * kernel only, 2 = shared-memory tiled kernel wherever it applies (N % 4 == 0, aligned dense
-     * operands, strictly ascending columns in every row), 3 = the same kernel with absent entries
-     * multiplied as zeros instead of being skipped under a mask: the fastest form from about 45 %
-     * nonzeros (17.0 against 15.8 TFLOP/s for row-gather at 50 %), bit-identical on finite data, but a
-     * non-finite value in B then reaches every row of its 64-row tile (0 * inf), which the reference
-     * loop and choices 0-2 do not do. */
+     * kernel only, 2 and 3 = shared-memory tiled kernel wherever it applies (N % 4 == 0, aligned dense
+     * operands, strictly ascending columns in every row; restricted by the threshold below only if
+     * the caller has set one).  3 is the form the automatic choice uses: absent entries are
+     * multiplied as zeros, except in chunks of B that hold an infinity or a NaN, which run under the
+     * presence masks, so that a non-finite value of B reaches exactly the rows that reference it, as
+     * in the reference loop.  2 runs every chunk under the masks (slower; kept for tests).  All
+     * choices give the same bits on the same input (apart from the sign of a zero sum, see the
+     * kernel). */
     DLSPM_OPT_SPMM_KERNEL = 1,
     /* Threshold of the automatic choice, in thousandths: the tiled kernel is taken for problems
-     * whose fraction of nonzeros is at least value/1000.  Default 1001, i.e. never: on B200 the
-     * row-gather kernel is still the faster one at every density measured, so the tiled kernel runs
-     * only when asked for (this option or DLSPM_OPT_SPMM_KERNEL = 2). */
+     * whose fraction of nonzeros is at least value/1000.  Default 450: on B200 the tiled kernel
+     * reaches 22.5 TFLOP/s on half-full problems against 15.8 for the row-gather kernel, and loses
+     * at 30 % nonzeros (13.9 against 17).  1001 = never; -1 = back to the default, as if never set. */
     DLSPM_OPT_TILE_MIN_DENSITY = 2
 } dlspm_option;
 int dlspm_set_option(dlspm_ctx *ctx, int option, int value);
@@ -313,6 +315,14 @@ void dlspm_free_host(void *p);
  * one). */
 int dlspm_sanity_check_csr_host(int M, int K, int N, int nnz, const int *row_offsets,
                                 const int *column_indices, char *why, size_t why_len);
+
+/* The same validation for CSR arrays in DEVICE memory (patterns generated or assembled on the device
+ * never pass the host check): one kernel over the offsets and the column indices, then the answer is
+ * read back (the call synchronises `stream`).  The kernels of this library trust their CSR arrays as
+ * the reference's do: a column index beyond K reads outside B.  Run this first on input that is not
+ * trusted; DLSPM_ERR_CSR and a one-line reason as above. */
+int dlspm_sanity_check_csr(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets,
+                           const int *column_indices, char *why, size_t why_len, void *stream);
 
 /* ---- seeded synthetic inputs (host and device) ------------------------------------------ */
 /* One counter-based generator (splitmix64 of seed, stream and element index) defines every

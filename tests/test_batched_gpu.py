@@ -274,7 +274,6 @@ def _run_prepared(pkg, ctx, dev, probs, kernel, min_density=None):
     import torch
 
     ctx.set_option(pkg.OPT_SPMM_KERNEL, kernel)
-    old_density = ctx.get_option(pkg.OPT_TILE_MIN_DENSITY)
     if min_density is not None:
         ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, min_density)
     try:
@@ -292,7 +291,7 @@ def _run_prepared(pkg, ctx, dev, probs, kernel, min_density=None):
         batch.close()
     finally:
         ctx.set_option(pkg.OPT_SPMM_KERNEL, pkg.SPMM_KERNEL_AUTO)
-        ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, old_density)
+        ctx.set_option(pkg.OPT_TILE_MIN_DENSITY, -1)  # back to the default
     return [o.cpu().numpy() for o in outs], info
 
 
@@ -456,3 +455,30 @@ def test_bounded_wait_reports_timeout_and_context_survives(pkg, oracle, ctx, dev
     bad, worst = oracle.violations(oracle.spmm(vals, ro, ci, B, M, N), Cd.cpu().numpy(),
                                    oracle.spmm_scale(vals, ro, ci, B, M, N), TOL)
     assert bad == 0, worst
+
+
+def test_device_side_csr_check(pkg, ctx, dev):
+    """dlspm_sanity_check_csr validates CSR arrays that live on the device with the host check's rules
+    and texts: a valid pattern passes; a column beyond K, a negative column, decreasing offsets, a
+    wrong last offset and a wrong first offset are each reported."""
+    M, K = 300, 200
+    ro, ci = csr_bernoulli(pkg, M, K, 0.1, 77)
+    nnz = int(ci.size)
+    assert ctx.sanity_check_csr(M, K, nnz, to_dev(ro, dev), to_dev(ci, dev)) == (pkg.OK, "")
+    empty = np.zeros(M + 1, dtype=np.int32)
+    assert ctx.sanity_check_csr(M, K, 0, to_dev(empty, dev), None)[0] == pkg.OK
+    bad = ci.copy(); bad[nnz // 2] = K
+    st, why = ctx.sanity_check_csr(M, K, nnz, to_dev(ro, dev), to_dev(bad, dev))
+    assert st == pkg.ERR_CSR and "a_column_indices[i] >= KSZ" in why and f"i = {nnz // 2}" in why
+    bad = ci.copy(); bad[3] = -1
+    assert ctx.sanity_check_csr(M, K, nnz, to_dev(ro, dev), to_dev(bad, dev))[0] == pkg.ERR_CSR
+    bad = ro.copy(); bad[10], bad[11] = bad[11], bad[10] - 1
+    st, why = ctx.sanity_check_csr(M, K, nnz, to_dev(bad, dev), to_dev(ci, dev))
+    assert st == pkg.ERR_CSR and "a_row_offsets" in why
+    bad = ro.copy(); bad[-1] += 1
+    st, why = ctx.sanity_check_csr(M, K, nnz, to_dev(bad, dev), to_dev(ci, dev))
+    assert st == pkg.ERR_CSR and why == "a_row_offsets[MSZ] != nnz."
+    bad = ro.copy(); bad[0] = 1
+    st, why = ctx.sanity_check_csr(M, K, nnz, to_dev(bad, dev), to_dev(ci, dev))
+    assert st == pkg.ERR_CSR and "a_row_offsets[0] != 0" in why
+    assert ctx.sanity_check_csr(2, 2, 5, to_dev(np.array([0, 2, 5], np.int32), dev), to_dev(np.zeros(5, np.int32), dev))[1] == "nnz is larger than matrix."
