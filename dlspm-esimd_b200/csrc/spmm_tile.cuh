@@ -35,6 +35,10 @@
 namespace dlspm {
 
 constexpr int kTileN = 256, kTileK = 32;
+#ifndef DLSPM_TILE_UNROLL
+#define DLSPM_TILE_UNROLL 8
+#endif
+constexpr int kTileUnroll = DLSPM_TILE_UNROLL;  // columns of a chunk per unrolled step of the multiply loop
 #ifndef DLSPM_TILE_CONSUMERS
 #define DLSPM_TILE_CONSUMERS 16
 #endif
@@ -393,7 +397,7 @@ __device__ __forceinline__ void tile_chunk_dense(const TileSmem &sm, int s, int 
 {
     const float *bs = &sm.Bs[s][0][lane * 4];
     const float *as = &sm.As[warp][buf][0][0];
-#pragma unroll 8
+#pragma unroll(kTileUnroll)
     for (int k = 0; k < kTileK; k++) {
         const float4 a0 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp);
         const float4 a1 = *reinterpret_cast<const float4 *>(as + k * kTileRowsPerWarp + 4);
