@@ -229,10 +229,43 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
     }
 }
 
+// Patterns of one to a few waves of thread blocks, as in the SDDMM launcher: two or four warps per row
+// make the waves finer where the last one would be nearly empty (6144 or 12288 rows).  A shared row
+// costs more here than in SDDMM (every warp loads the row of C, partial rows are combined through
+// shared memory): 15 % per doubling in the estimate.
+inline int fused_wave_shift(long long blocks, long long resident, double avg_row)
+{
+    if (blocks <= resident || blocks > 8 * resident) return 0;
+    int best = 0;
+    double best_cost = 1e30;
+    for (int s = 0; s <= 2 && avg_row > 32.0 * (1 << s); s++) {
+        const long long waves = ((blocks << s) + resident - 1) / resident;
+        const double cost = (double)waves / (double)(1 << s) * (1.0 + 0.15 * s);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = s;
+        }
+    }
+    return best;
+}
+
 template <int G, int R, int MODE>
 void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
-                 int M, int chunks, float scale, int split_shift, int sm_count, cudaStream_t st)
+                 int M, int chunks, float scale, int split_shift, int sm_count, cudaStream_t st, double avg_row = 0.0)
 {
+    if (split_shift == 0 && avg_row > 0.0) {
+        static int per_sm = 0;  // resident blocks of the plain build of this layout
+        if (per_sm == 0) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fused_rows_kernel<G, R, MODE>, kWarps * 32, 0) != cudaSuccess) {
+                (void)cudaGetLastError();
+                n = 4;
+            }
+            per_sm = n > 0 ? n : 4;
+            if (G == 8 && R == 1) per_sm = 8;  // this layout has a capped build for eight resident blocks (below)
+        }
+        split_shift = fused_wave_shift(((long long)M + kWarps - 1) / kWarps, (long long)per_sm * sm_count, avg_row);
+    }
     if (split_shift > 0) {
         const long long warps = (long long)M << split_shift;
         const size_t smem = sizeof(float4) * (size_t)kWarps * G * R;
@@ -292,12 +325,12 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     if (vec == 4 && sddmm_layout(N / 4, &G, &R)) {
         const int chunks = N / 4;
         const int shift = fused_split_shift(ctx, M, N, nnz);
-        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
-        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
-        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
-        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
-        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
-        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st);
+        if (G == 8 && R == 1) launch_fast<8, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 8 && R == 2) launch_fast<8, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 8 && R == 4) launch_fast<8, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+        else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+        else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
     } else {
         fused_generic_kernel<MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N, scale);
     }
