@@ -9,6 +9,7 @@
 
 // staging slots of the pipelined host-buffer calls (copy in, launch, copy out overlap across slots)
 constexpr int kPipeSlots = 4;
+constexpr int kSideStreams = 9;
 
 struct dlspm_ctx {
     int device;
@@ -33,6 +34,11 @@ struct dlspm_ctx {
     int pipeline_ready;
     void *pinned;  // pinned host memory for the launch tables of the pipelined batch
     size_t pinned_bytes;
+    // side streams on which the launches of one grouped SDDMM / fused call run side by side (created
+    // on first use); events to fork them from the caller's stream and to join them again
+    cudaStream_t side_stream[kSideStreams];
+    cudaEvent_t side_fork, side_join[kSideStreams];
+    int side_ready;
     long long host_copies;  // cudaMemcpyAsync calls issued by the pipelined host-buffer batch so far
 };
 

@@ -80,6 +80,13 @@ extern "C" int dlspm_destroy(dlspm_ctx *ctx)
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->side_ready) {
+        for (int i = 0; i < kSideStreams; i++) {
+            cudaStreamDestroy(ctx->side_stream[i]);
+            cudaEventDestroy(ctx->side_join[i]);
+        }
+        cudaEventDestroy(ctx->side_fork);
+    }
     if (ctx->pipeline_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);

@@ -20,8 +20,9 @@ using namespace dlspm;
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kClasses = 8;  // the six (G, R) layouts of sddmm_layout, then SDDMM rows beyond 1024 floats in segments of 1024 / 512
-constexpr int kOpSddmm = 0, kOpFused = 1, kOpSddmmLong = 2;
+constexpr int kClasses = 10;  // the six (G, R) layouts of sddmm_layout, then SDDMM rows beyond 1024 floats in segments of
+                              // 1024 / 512 floats, one warp per row (6, 7) or rows shared between warps (8, 9)
+constexpr int kOpSddmm = 0, kOpFused = 1, kOpSddmmLong = 2, kOpSddmmLongShared = 3;
 
 struct RowProblem {
     const int *row_offsets;
@@ -33,23 +34,27 @@ struct RowProblem {
     float *out;         // out_values (SDDMM) or E (fused)
     int M;
     int chunks;         // N / 4
+    int shift;          // SDDMM: 1 << shift warps share a row (its passes in turn; for rows beyond 1024
+                        // floats the nonzeros inside every pass), see choose_sharing
 };
 
+// `sub` of 1 << p.shift warps that share the row: this warp takes the passes sub, sub + (1 << shift), ...
 template <int G, int R>
-__device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int lane)
+__device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int sub, int lane)
 {
     const int g = lane / G, t = lane % G;
-    const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
+    const int stride = 32 << p.shift;
+    const int start = __ldg(p.row_offsets + row) + 32 * sub, end = __ldg(p.row_offsets + row + 1);
     if (start >= end) return;
     const float4 *lhs4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
     const float4 *rhs4 = reinterpret_cast<const float4 *>(p.b);
     float4 a[R];
     load_row_chunks<G, R>(lhs4, p.chunks, t, a);
     int col_next = start + lane < end ? __ldg(p.cols + start + lane) : -1;
-    for (int base = start; base < end; base += 32) {
+    for (int base = start; base < end; base += stride) {
         const int q = base + lane;
         const int col = col_next;
-        col_next = q + 32 < end ? __ldg(p.cols + q + 32) : -1;
+        col_next = q + stride < end ? __ldg(p.cols + q + stride) : -1;
         const float r = sddmm_pass<G, R>(a, rhs4, p.chunks, col, g, t);
         if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * r : r;
     }
@@ -57,10 +62,12 @@ __device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int 
 
 // Inner dimension beyond 1024: the partial dot products of a pass are accumulated over segments of
 // 32*R float4 of the two rows and reduced once per pass, as in the single-matrix kernel for long rows.
-template <int R>
-__device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row, int lane)
+// `sub` of 1 << p.shift warps that share the row: this warp takes every (1 << shift)-th nonzero of a pass.
+template <int R, bool KSPLIT>
+__device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row, int sub, int lane)
 {
     constexpr int G = 32, kSeg = G * R;
+    const int kmask = (1 << p.shift) - 1;
     const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
     if (start >= end) return;
     const float4 *lhs4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
@@ -77,10 +84,10 @@ __device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row,
             const int len = min(kSeg, p.chunks - seg);
             float4 a[R];
             load_row_chunks<G, R>(lhs4 + seg, len, lane, a);
-            sddmm_accumulate<G, R, false>(part, a, rhs4 + seg, len, p.chunks, col, 0, lane);
+            sddmm_accumulate<G, R, KSPLIT>(part, a, rhs4 + seg, len, p.chunks, col, 0, lane, kmask, sub);
         }
         group_transpose_reduce<G>(part, lane);
-        if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * part[0] : part[0];
+        if (q < end && (!KSPLIT || (lane & kmask) == sub)) p.out[q] = p.mask ? __ldg(p.mask + q) * part[0] : part[0];
     }
 }
 
@@ -131,10 +138,12 @@ rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__
             else hi = mid - 1;
         }
         const RowProblem p = problems[lo];
-        const int row = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
+        const int slot = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
+        const int row = slot >> p.shift, sub = slot & ((1 << p.shift) - 1);  // fused: shift is 0
         if (row < p.M) {
-            if constexpr (OP == kOpSddmmLong) sddmm_one_row_long<R>(p, row, lane);
-            else if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, lane);
+            if constexpr (OP == kOpSddmmLongShared) sddmm_one_row_long<R, true>(p, row, sub, lane);
+            else if constexpr (OP == kOpSddmmLong) sddmm_one_row_long<R, false>(p, row, 0, lane);
+            else if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, sub, lane);
             else fused_one_row<G, R>(p, row, lane);
         }
     }
@@ -171,15 +180,63 @@ int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, cons
     case 4: return launch_class<32, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     case 5: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     case 6: return launch_class<32, 8, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    default: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 7: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 8: return launch_class<32, 8, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    default: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
     }
+}
+
+int side_streams_init(dlspm_ctx *ctx)
+{
+    if (ctx->side_ready) return DLSPM_OK;
+    for (int i = 0; i < kSideStreams; i++) {
+        DLSPM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->side_stream[i], cudaStreamNonBlocking));
+        DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->side_join[i], cudaEventDisableTiming));
+    }
+    DLSPM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
+    ctx->side_ready = 1;
+    return DLSPM_OK;
 }
 
 struct HostEntry {
     RowProblem p;
     double work;
+    double avg_row;
     int index;
 };
+
+// SDDMM classes with too few rows to fill the device with one warp per row: rows are shared between
+// 2, 4 or 8 warps, as the single-matrix launcher does for lone patterns (the outputs of different
+// nonzeros are independent, so nothing is combined).  Register-resident rows (classes 0..5) deal out
+// the passes of 32 nonzeros, as long as a warp keeps about one pass; rows beyond 1024 floats (classes
+// 6, 7) deal out the nonzeros inside every pass and move to the classes 8, 9, whose kernels carry the
+// extra test.
+void choose_sharing(const dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses])
+{
+    const long long want = (long long)ctx->sm_count * 32;
+    for (int c = 0; c < 8; c++) {
+        std::vector<HostEntry> &v = by_class[c];
+        long long rows = 0;
+        for (const HostEntry &e : v) rows += e.p.M;
+        if (v.empty() || rows * 4 >= want * 3) continue;
+        int cls_shift = 0;
+        while (cls_shift < 3 && (rows << cls_shift) < want) cls_shift++;
+        for (HostEntry &e : v) {
+            int s = 0;
+            if (c < 6) {
+                while (s < cls_shift && e.avg_row > 32.0 * (1 << s)) s++;
+            } else {
+                s = cls_shift;
+            }
+            e.p.shift = s;
+        }
+        if (c >= 6) {  // shared long rows run on the kernels with the extra test
+            for (HostEntry &e : v)
+                if (e.p.shift > 0) by_class[c + 2].push_back(e);
+            v.erase(std::remove_if(v.begin(), v.end(), [](const HostEntry &e) { return e.p.shift > 0; }), v.end());
+        }
+    }
+}
 
 // Device layout of the tables of one call inside `tables`: per class its problems, then its tile
 // index, then all counters.
@@ -230,7 +287,7 @@ int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses]
         for (size_t i = 0; i < v.size(); i++) {
             tab[i] = v[i].p;
             starts[i] = run;
-            run += dlspm_ceil_div(v[i].p.M, kWarps);
+            run += (long long)((((long long)v[i].p.M << v[i].p.shift) + kWarps - 1) / kWarps);
         }
         starts[v.size()] = run;
         tiles[c] = run;
@@ -241,12 +298,30 @@ int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses]
     unsigned long long *d_counters = (unsigned long long *)(base + image_bytes);
     DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(base, img, image_bytes, cudaMemcpyHostToDevice, st));
     DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(d_counters, 0, 256, st));
+    // The launches of the classes are independent: the first runs on the caller's stream, the others
+    // on side streams forked from it after the table copy and joined back afterwards, so that a batch
+    // with several inner dimensions takes about as long as its slowest class, not the sum.
+    int live = 0;
+    for (int c = 0; c < kClasses; c++) live += (!by_class[c].empty() && tiles[c] > 0) ? 1 : 0;
+    if (live > 1) {
+        int rc = side_streams_init(ctx);
+        if (rc) return rc;
+        DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->side_fork, st));
+    }
+    int used = 0;
     for (int c = 0; c < kClasses; c++) {
         if (by_class[c].empty() || tiles[c] == 0) continue;
+        cudaStream_t sc = used == 0 ? st : ctx->side_stream[used - 1];
+        if (used > 0) DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(sc, ctx->side_fork, 0));
         int rc = launch_class_by_index<OP>(ctx, c, (const RowProblem *)(base + tab_off[c]),
                                            (const long long *)(base + st_off[c]), (int)by_class[c].size(), tiles[c],
-                                           d_counters + c, st);
+                                           d_counters + c, sc);
         if (rc) return rc;
+        if (used > 0) {
+            DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->side_join[used - 1], sc));
+            DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(st, ctx->side_join[used - 1], 0));
+        }
+        used++;
     }
     return DLSPM_OK;
 }
@@ -288,7 +363,8 @@ int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem 
         const bool wide = q.N > 0 && dlspm_vec_width(q.N, q.lhs, q.rhs) == 4;
         if (wide) {
             HostEntry e;
-            e.p = RowProblem{q.row_offsets, q.column_indices, q.lhs, q.rhs, nullptr, q.mask_values, q.out_values, q.M, q.N / 4};
+            e.p = RowProblem{q.row_offsets, q.column_indices, q.lhs, q.rhs, nullptr, q.mask_values, q.out_values, q.M, q.N / 4, 0};
+            e.avg_row = (double)q.nnz / (double)q.M;
             e.work = (double)q.nnz * q.N;
             e.index = i;
             // beyond the register-resident layouts: segments of 1024 floats, of 512 from N = 2052 on
@@ -301,6 +377,7 @@ int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem 
             if (rc) return rc;
         }
     }
+    choose_sharing(ctx, by_class);
     return rows_batched_at<kOpSddmm>(ctx, by_class, tables, pinned, st);
 }
 
@@ -320,7 +397,8 @@ int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem 
         int G = 0, R = 0;
         if (dlspm_vec_width(q.N, q.C, q.B, q.D, q.E) == 4 && sddmm_layout(q.N / 4, &G, &R)) {
             HostEntry e;
-            e.p = RowProblem{q.row_offsets, q.column_indices, q.C, q.B, q.D, nullptr, q.E, q.M, q.N / 4};
+            e.p = RowProblem{q.row_offsets, q.column_indices, q.C, q.B, q.D, nullptr, q.E, q.M, q.N / 4, 0};
+            e.avg_row = 0.0;
             e.work = (double)q.nnz * q.N + (double)q.M;  // rows without entries still cost a store
             e.index = i;
             by_class[layout_class(G, R)].push_back(e);
