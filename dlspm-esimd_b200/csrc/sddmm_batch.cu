@@ -91,21 +91,52 @@ __device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row,
     }
 }
 
+// `sub` of 1 << p.shift warps of the thread block that share the row: this warp takes the passes sub,
+// sub + (1 << shift), ...; the partial rows of the others are handed to the row's first warp through
+// `part` ([kWarps][G * R] float4 of shared memory) and added in a fixed order, as in the single-matrix
+// kernel for patterns with few rows.  Every warp of the block calls this for the same tile (warps
+// without a row included), because of the barrier inside.
 template <int G, int R>
-__device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int lane)
+__device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int sub, bool has_row, int warp, int lane,
+                                              float4 *part)
 {
     const int g = lane / G, t = lane % G;
-    const float4 *c4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
-    float4 q[R];
-    load_row_chunks<G, R>(c4, p.chunks, t, q);
     float4 acc[R];
 #pragma unroll
     for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float run_max = -INFINITY, run_sum = 0.f;
-    fused_row_passes<G, R, kPlain>(p.cols, q, reinterpret_cast<const float4 *>(p.b),
-                                   reinterpret_cast<const float4 *>(p.d), p.chunks, __ldg(p.row_offsets + row),
-                                   __ldg(p.row_offsets + row + 1), 32, 1.f, lane, acc, run_max, run_sum);
-    if (g == 0) {  // rows without entries are written as zeros
+    if (has_row) {
+        const int start = __ldg(p.row_offsets + row) + 32 * sub, end = __ldg(p.row_offsets + row + 1);
+        if (start < end) {
+            const float4 *c4 = reinterpret_cast<const float4 *>(p.a) + (size_t)row * (size_t)p.chunks;
+            float4 q[R];
+            load_row_chunks<G, R>(c4, p.chunks, t, q);
+            float run_max = -INFINITY, run_sum = 0.f;
+            fused_row_passes<G, R, kPlain>(p.cols, q, reinterpret_cast<const float4 *>(p.b),
+                                           reinterpret_cast<const float4 *>(p.d), p.chunks, start, end, 32 << p.shift, 1.f,
+                                           lane, acc, run_max, run_sum);
+        }
+    }
+    if (p.shift > 0) {  // uniform over the block
+        if (sub != 0 && g == 0) {
+#pragma unroll
+            for (int r = 0; r < R; r++) part[warp * (G * R) + r * G + t] = acc[r];
+        }
+        __syncthreads();
+        if (sub == 0 && g == 0) {
+            for (int o = 1; o < (1 << p.shift); o++) {
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const float4 v = part[(warp + o) * (G * R) + r * G + t];
+                    acc[r].x += v.x;
+                    acc[r].y += v.y;
+                    acc[r].z += v.z;
+                    acc[r].w += v.w;
+                }
+            }
+        }
+        __syncthreads();  // `part` is reused by the block's next tile
+    }
+    if (has_row && sub == 0 && g == 0) {  // rows without entries are written as zeros
         float4 *e4 = reinterpret_cast<float4 *>(p.out) + (size_t)row * (size_t)p.chunks;
 #pragma unroll
         for (int r = 0; r < R; r++) {
@@ -123,6 +154,7 @@ rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__
                     unsigned long long *counter)
 {
     __shared__ unsigned long long s_tile;
+    __shared__ float4 part[OP == kOpFused ? kWarps * G * R : 1];  // partial rows of warps that share a row (fused only)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total = tile_start[count];
     for (;;) {
@@ -139,12 +171,13 @@ rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__
         }
         const RowProblem p = problems[lo];
         const int slot = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
-        const int row = slot >> p.shift, sub = slot & ((1 << p.shift) - 1);  // fused: shift is 0
-        if (row < p.M) {
+        const int row = slot >> p.shift, sub = slot & ((1 << p.shift) - 1);
+        if constexpr (OP == kOpFused) {
+            fused_one_row<G, R>(p, row, sub, row < p.M, warp, lane, part);
+        } else if (row < p.M) {
             if constexpr (OP == kOpSddmmLongShared) sddmm_one_row_long<R, true>(p, row, sub, lane);
             else if constexpr (OP == kOpSddmmLong) sddmm_one_row_long<R, false>(p, row, 0, lane);
-            else if constexpr (OP == kOpSddmm) sddmm_one_row<G, R>(p, row, sub, lane);
-            else fused_one_row<G, R>(p, row, lane);
+            else sddmm_one_row<G, R>(p, row, sub, lane);
         }
     }
 }
@@ -205,9 +238,10 @@ struct HostEntry {
     int index;
 };
 
-// SDDMM classes with too few rows to fill the device with one warp per row: rows are shared between
-// 2, 4 or 8 warps, as the single-matrix launcher does for lone patterns (the outputs of different
-// nonzeros are independent, so nothing is combined).  Register-resident rows (classes 0..5) deal out
+// Classes with too few rows to fill the device with one warp per row: rows are shared between 2, 4 or
+// 8 warps, as the single-matrix launchers do for lone patterns (SDDMM: the outputs of different
+// nonzeros are independent, nothing is combined; fused chain: partial rows are added through shared
+// memory).  Register-resident rows (classes 0..5) deal out
 // the passes of 32 nonzeros, as long as a warp keeps about one pass; rows beyond 1024 floats (classes
 // 6, 7) deal out the nonzeros inside every pass and move to the classes 8, 9, whose kernels carry the
 // extra test.
@@ -398,7 +432,7 @@ int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem 
         if (dlspm_vec_width(q.N, q.C, q.B, q.D, q.E) == 4 && sddmm_layout(q.N / 4, &G, &R)) {
             HostEntry e;
             e.p = RowProblem{q.row_offsets, q.column_indices, q.C, q.B, q.D, nullptr, q.E, q.M, q.N / 4, 0};
-            e.avg_row = 0.0;
+            e.avg_row = (double)q.nnz / (double)q.M;
             e.work = (double)q.nnz * q.N + (double)q.M;  // rows without entries still cost a store
             e.index = i;
             by_class[layout_class(G, R)].push_back(e);
@@ -408,6 +442,7 @@ int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem 
             if (rc) return rc;
         }
     }
+    choose_sharing(ctx, by_class);  // classes 6..9 are never filled for the fused chain
     return rows_batched_at<kOpFused>(ctx, by_class, tables, pinned, st);
 }
 
