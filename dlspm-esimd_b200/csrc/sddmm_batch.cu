@@ -4,8 +4,9 @@
 // launches of the reference's batch scripts (SDDMM/batch-run-sddmm_fromfile:31-47,
 // FUSED/batch-run-fused:22-34) spend more time between kernels than in them.  Here all problems of a
 // batch that share a register layout (group width G and chunks per lane R, which follow from the
-// inner dimension, see sddmm_device.cuh) run in ONE persistent launch: thread blocks pull tiles of
-// eight rows from a device counter, one warp per row, and every row is processed exactly as in the
+// inner dimension, see sddmm_device.cuh) run in ONE persistent launch: warps pull rows from a device
+// counter (thread blocks pull tiles of eight where the fused chain shares rows between warps), one
+// warp per row, and every row is processed exactly as in the
 // single-matrix kernels (same passes, same butterfly, same order of additions), so results have the
 // same bits.  A batch with one inner dimension is one launch; a mixed batch is at most six.
 #include <algorithm>
@@ -96,7 +97,7 @@ __device__ __forceinline__ void sddmm_one_row_long(const RowProblem &p, int row,
 // `part` ([kWarps][G * R] float4 of shared memory) and added in a fixed order, as in the single-matrix
 // kernel for patterns with few rows.  Every warp of the block calls this for the same tile (warps
 // without a row included), because of the barrier inside.
-template <int G, int R>
+template <int G, int R, bool SHARED>
 __device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int sub, bool has_row, int warp, int lane,
                                               float4 *part)
 {
@@ -116,7 +117,7 @@ __device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int 
                                            lane, acc, run_max, run_sum);
         }
     }
-    if (p.shift > 0) {  // uniform over the block
+    if (SHARED && p.shift > 0) {  // uniform over the block
         if (sub != 0 && g == 0) {
 #pragma unroll
             for (int r = 0; r < R; r++) part[warp * (G * R) + r * G + t] = acc[r];
@@ -146,22 +147,38 @@ __device__ __forceinline__ void fused_one_row(const RowProblem &p, int row, int 
     }
 }
 
-// Persistent thread blocks pull tile numbers (eight rows of one problem) from a device counter;
-// tile_start[i] is the first tile of problem i, tile_start[count] the total.
-template <int G, int R, int OP>
+// Persistent launch over the rows of all problems of one class.  A tile is eight slots (rows, or
+// parts of rows where warps share them) of one problem; tile_start[i] is the first tile of problem i,
+// tile_start[count] the total.  BLOCK: a thread block pulls a tile from the device counter and its
+// warps take the eight slots together, which the fused chain needs where warps share rows (partial
+// rows meet in shared memory behind a barrier).  Otherwise every warp pulls one slot at a time for
+// itself (the counter counts slots): no barrier, so a warp with a short row does not wait for the
+// longest row of its tile.
+template <int G, int R, int OP, bool BLOCK>
 __global__ void __launch_bounds__(kWarps * 32)
 rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__restrict__ tile_start, int count,
                     unsigned long long *counter)
 {
     __shared__ unsigned long long s_tile;
-    __shared__ float4 part[OP == kOpFused ? kWarps * G * R : 1];  // partial rows of warps that share a row (fused only)
+    __shared__ float4 part[OP == kOpFused && BLOCK ? kWarps * G * R : 1];  // partial rows of warps that share a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total = tile_start[count];
     for (;;) {
-        if (threadIdx.x == 0) s_tile = atomicAdd(counter, 1ull);
-        __syncthreads();
-        const long long tile = (long long)s_tile;
-        __syncthreads();
+        long long tile;
+        int in_tile;
+        if constexpr (BLOCK) {
+            if (threadIdx.x == 0) s_tile = atomicAdd(counter, 1ull);
+            __syncthreads();
+            tile = (long long)s_tile;
+            in_tile = warp;
+            __syncthreads();
+        } else {
+            unsigned long long s = 0;
+            if (lane == 0) s = atomicAdd(counter, 1ull);
+            s = __shfl_sync(0xffffffffu, s, 0);
+            tile = (long long)(s / kWarps);
+            in_tile = (int)(s % kWarps);
+        }
         if (tile >= total) break;
         int lo = 0, hi = count - 1;  // last problem whose first tile is <= tile
         while (lo < hi) {
@@ -170,10 +187,10 @@ rows_batched_kernel(const RowProblem *__restrict__ problems, const long long *__
             else hi = mid - 1;
         }
         const RowProblem p = problems[lo];
-        const int slot = (int)(tile - __ldg(tile_start + lo)) * kWarps + warp;
+        const int slot = (int)(tile - __ldg(tile_start + lo)) * kWarps + in_tile;
         const int row = slot >> p.shift, sub = slot & ((1 << p.shift) - 1);
         if constexpr (OP == kOpFused) {
-            fused_one_row<G, R>(p, row, sub, row < p.M, warp, lane, part);
+            if (BLOCK || row < p.M) fused_one_row<G, R, BLOCK>(p, row, sub, row < p.M, warp, lane, part);
         } else if (row < p.M) {
             if constexpr (OP == kOpSddmmLongShared) sddmm_one_row_long<R, true>(p, row, sub, lane);
             else if constexpr (OP == kOpSddmmLong) sddmm_one_row_long<R, false>(p, row, 0, lane);
@@ -189,33 +206,46 @@ int layout_class(int G, int R)
     return R == 4 ? 4 : 5;
 }
 
-template <int G, int R, int OP>
-int launch_class(dlspm_ctx *ctx, const RowProblem *d_tab, const long long *d_starts, int count, long long tiles,
-                 unsigned long long *d_counter, cudaStream_t st)
+template <int G, int R, int OP, bool BLOCK>
+int launch_kernel(dlspm_ctx *ctx, const RowProblem *d_tab, const long long *d_starts, int count, long long tiles,
+                  unsigned long long *d_counter, cudaStream_t st)
 {
     int per_sm = 0;
-    DLSPM_CUDA_TRY(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rows_batched_kernel<G, R, OP>, kWarps * 32, 0));
+    DLSPM_CUDA_TRY(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rows_batched_kernel<G, R, OP, BLOCK>,
+                                                                      kWarps * 32, 0));
     const long long want = std::min<long long>(tiles, (long long)ctx->sm_count * std::max(per_sm, 1));
-    rows_batched_kernel<G, R, OP><<<(unsigned)want, kWarps * 32, 0, st>>>(d_tab, d_starts, count, d_counter);
+    rows_batched_kernel<G, R, OP, BLOCK><<<(unsigned)want, kWarps * 32, 0, st>>>(d_tab, d_starts, count, d_counter);
     DLSPM_CUDA_TRY(ctx, cudaGetLastError());
     return DLSPM_OK;
 }
 
+// `shared`: some problem of the class has warps sharing rows.  Only the fused chain needs the
+// block-wide form for that.
+template <int G, int R, int OP>
+int launch_class(dlspm_ctx *ctx, const RowProblem *d_tab, const long long *d_starts, int count, long long tiles,
+                 unsigned long long *d_counter, bool shared, cudaStream_t st)
+{
+    if constexpr (OP == kOpFused) {
+        if (shared) return launch_kernel<G, R, OP, true>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    }
+    return launch_kernel<G, R, OP, false>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+}
+
 template <int OP>
 int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, const long long *d_starts, int count,
-                          long long tiles, unsigned long long *d_counter, cudaStream_t st)
+                          long long tiles, unsigned long long *d_counter, bool shared, cudaStream_t st)
 {
     switch (cls) {
-    case 0: return launch_class<8, 1, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 1: return launch_class<8, 2, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 2: return launch_class<8, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 3: return launch_class<16, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 4: return launch_class<32, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 5: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 6: return launch_class<32, 8, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 7: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    case 8: return launch_class<32, 8, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
-    default: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, st);
+    case 0: return launch_class<8, 1, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 1: return launch_class<8, 2, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 2: return launch_class<8, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 3: return launch_class<16, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 4: return launch_class<32, 4, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 5: return launch_class<32, 8, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 6: return launch_class<32, 8, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 7: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 8: return launch_class<32, 8, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    default: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     }
 }
 
@@ -309,6 +339,7 @@ int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses]
     }
     size_t tab_off[kClasses], st_off[kClasses];
     long long tiles[kClasses];
+    bool shared[kClasses];
     size_t toff = 0, soff = tab_bytes;
     for (int c = 0; c < kClasses; c++) {
         std::vector<HostEntry> &v = by_class[c];
@@ -318,8 +349,10 @@ int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses]
         RowProblem *tab = (RowProblem *)(img + toff);
         long long *starts = (long long *)(img + soff);
         long long run = 0;
+        shared[c] = false;
         for (size_t i = 0; i < v.size(); i++) {
             tab[i] = v[i].p;
+            shared[c] = shared[c] || v[i].p.shift > 0;
             starts[i] = run;
             run += (long long)((((long long)v[i].p.M << v[i].p.shift) + kWarps - 1) / kWarps);
         }
@@ -349,7 +382,7 @@ int rows_batched_at(dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses]
         if (used > 0) DLSPM_CUDA_TRY(ctx, cudaStreamWaitEvent(sc, ctx->side_fork, 0));
         int rc = launch_class_by_index<OP>(ctx, c, (const RowProblem *)(base + tab_off[c]),
                                            (const long long *)(base + st_off[c]), (int)by_class[c].size(), tiles[c],
-                                           d_counters + c, sc);
+                                           d_counters + c, shared[c], sc);
         if (rc) return rc;
         if (used > 0) {
             DLSPM_CUDA_TRY(ctx, cudaEventRecord(ctx->side_join[used - 1], sc));
