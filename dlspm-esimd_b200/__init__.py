@@ -86,6 +86,7 @@ _SIGNATURES = {
     "dlspm_fused_attention_f32": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, C.c_float, C.c_uint, _P]),
     "dlspm_plan_create": (_I, [_P, _I, _I, _I, _P, _P, _P, C.POINTER(_P)]),
     "dlspm_plan_destroy": (_I, [_P]),
+    "dlspm_plan_row_order": (_I, [_P, _P, _P]),
     "dlspm_spmm_batched_f32": (_I, [_P, _I, C.POINTER(Problem), _P]),
     "dlspm_sddmm_batched_f32": (_I, [_P, _I, C.POINTER(SddmmProblem), _P]),
     "dlspm_fused_batched_f32": (_I, [_P, _I, C.POINTER(FusedProblem), _P]),
@@ -326,7 +327,7 @@ class Context:
             self.handle, M, K, nnz, _dev_ptr(row_offsets, torch.int32, "row_offsets"),
             _dev_ptr(column_indices, torch.int32, "column_indices"), _stream_ptr(stream), C.byref(h)),
             "dlspm_plan_create", self)
-        return Plan(self, h)
+        return Plan(self, h, M)
 
     def spmm_planned(self, plan, N, values, row_offsets, column_indices, B, Cout, stream=None) -> None:
         import torch
@@ -504,8 +505,16 @@ class DeviceArray:
 
 
 class Plan:
-    def __init__(self, ctx: Context, handle):
-        self.ctx, self.handle = ctx, handle
+    def __init__(self, ctx: Context, handle, M: int = 0):
+        self.ctx, self.handle, self.M = ctx, handle, M
+
+    def row_order(self, stream=None) -> np.ndarray:
+        """The plan's row order as a host array (dlspm_plan_row_order)."""
+        out = np.empty(self.M, dtype=np.int32)
+        if self.M:
+            _check(self.ctx.lib.dlspm_plan_row_order(self.handle, out.ctypes.data_as(_P), _stream_ptr(stream)),
+                   "dlspm_plan_row_order", self.ctx)
+        return out
 
     def close(self) -> None:
         if self.handle:

@@ -432,16 +432,26 @@ constexpr int kBins = 33;  // bin b holds rows with 2^(b-1) <= length < 2^b; bin
 
 __device__ __forceinline__ int length_bin(int len) { return len <= 0 ? 0 : 32 - __clz(len); }
 
-// info[0..32] = rows per bin, info[33] = 1 while every row is sorted, info[34] = longest row
-__global__ void plan_hist_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
-                                 int M, int *info)
+// Rows are placed in a fixed order: bins from the longest rows to the shortest, inside a bin by
+// ascending row number.  Every thread block owns a contiguous range of `span` rows; it counts its
+// rows per bin (plan_hist_kernel), a scan over (bin, block) gives the first slot of every block in
+// every bin (plan_scan_kernel), and the block then places its rows chunk by chunk, its warps one
+// after the other, each row at its rank among the rows of the same bin before it
+// (plan_scatter_kernel).  No slot is handed out by a global atomic, so the order, and with it the
+// timing of the kernels that walk it, is the same in every run.
+//
+// info[0..32] = rows per bin, info[33] = 1 while every row is sorted, info[34] = longest row;
+// block_hist[block * kBins + bin] = rows of the block in the bin.
+__global__ void __launch_bounds__(256) plan_hist_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                                                        int M, int span, int *info, int *__restrict__ block_hist)
 {
     __shared__ int hist[kBins];
     __shared__ int s_sorted, s_max;
     if (threadIdx.x < kBins) hist[threadIdx.x] = 0;
     if (threadIdx.x == 0) { s_sorted = 1; s_max = 0; }
     __syncthreads();
-    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
+    const int first = blockIdx.x * span, last = min(first + span, M);
+    for (int r = first + threadIdx.x; r < last; r += blockDim.x) {
         const int s = row_offsets[r], e = row_offsets[r + 1];
         atomicAdd(&hist[length_bin(e - s)], 1);
         atomicMax(&s_max, e - s);
@@ -450,31 +460,71 @@ __global__ void plan_hist_kernel(const int *__restrict__ row_offsets, const int 
         if (!sorted) s_sorted = 0;
     }
     __syncthreads();
-    if (threadIdx.x < kBins && hist[threadIdx.x]) atomicAdd(&info[threadIdx.x], hist[threadIdx.x]);
+    if (threadIdx.x < kBins) block_hist[blockIdx.x * kBins + threadIdx.x] = hist[threadIdx.x];
     if (threadIdx.x == 0) {
         if (!s_sorted) atomicAnd(&info[kBins], 0);
         atomicMax(&info[kBins + 1], s_max);
     }
 }
 
-// cursor[b] = first slot of bin b when bins are laid out from the longest to the shortest
-__global__ void plan_scan_kernel(const int *info, int *cursor)
+// cursor[block * kBins + bin] = first slot of the block's rows of the bin, bins laid out from the
+// longest to the shortest and blocks in order inside a bin; info[bin] = rows of the bin.  One thread
+// block of 64 threads: thread t sums bin t over the blocks, then the bins are scanned.
+__global__ void plan_scan_kernel(const int *__restrict__ block_hist, int blocks, int *info, int *__restrict__ cursor)
 {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
+    __shared__ int total[kBins], first[kBins];
+    const int bin = threadIdx.x;
+    if (bin < kBins) {
+        int run = 0;
+        for (int b = 0; b < blocks; b++) run += block_hist[b * kBins + bin];
+        total[bin] = run;
+        info[bin] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
         int run = 0;
         for (int b = kBins - 1; b >= 0; b--) {
-            cursor[b] = run;
-            run += info[b];
+            first[b] = run;
+            run += total[b];
+        }
+    }
+    __syncthreads();
+    if (bin < kBins) {
+        int run = first[bin];
+        for (int b = 0; b < blocks; b++) {
+            cursor[b * kBins + bin] = run;
+            run += block_hist[b * kBins + bin];
         }
     }
 }
 
-__global__ void plan_scatter_kernel(const int *__restrict__ row_offsets, int M, int *cursor,
-                                    int *__restrict__ row_order)
+__global__ void __launch_bounds__(256) plan_scatter_kernel(const int *__restrict__ row_offsets, int M, int span,
+                                                           const int *__restrict__ cursor, int *__restrict__ row_order)
 {
-    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < M; r += gridDim.x * blockDim.x) {
-        const int b = length_bin(row_offsets[r + 1] - row_offsets[r]);
-        row_order[atomicAdd(&cursor[b], 1)] = r;
+    __shared__ int next[kBins];  // next free slot of every bin for this block
+    if (threadIdx.x < kBins) next[threadIdx.x] = cursor[blockIdx.x * kBins + threadIdx.x];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first = blockIdx.x * span, last = min(first + span, M);
+    for (int base = first; base < last; base += blockDim.x) {  // same trip count for the whole block
+        const int r = base + threadIdx.x;
+        const bool have = r < last;
+        const int bin = have ? length_bin(row_offsets[r + 1] - row_offsets[r]) : 0;
+        const unsigned active = __ballot_sync(0xffffffffu, have);
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) {
+            if (warp == w && have) {
+                const unsigned peers = __match_any_sync(active, bin);  // lanes of this warp with a row of the same bin
+                const int leader = __ffs(peers) - 1;
+                int slot = 0;
+                if (lane == leader) {
+                    slot = next[bin];
+                    next[bin] = slot + __popc(peers);
+                }
+                slot = __shfl_sync(peers, slot, leader);
+                row_order[slot + __popc(peers & ((1u << lane) - 1u))] = r;
+            }
+            __syncthreads();
+        }
     }
 }
 
@@ -503,25 +553,30 @@ extern "C" int dlspm_plan_create(dlspm_ctx *ctx, int M, int K, int nnz, const in
         *out = plan;
         return DLSPM_OK;
     }
-    int *work = nullptr;  // [0..34] info, [40..72] cursors
+    // every thread block owns `span` consecutive rows (a multiple of its 256 threads)
+    const int blocks_max = std::max(1, std::min(dlspm_ceil_div(M, 256), ctx->sm_count * 8));
+    const int span = dlspm_ceil_div(dlspm_ceil_div(M, blocks_max), 256) * 256;
+    const int blocks = dlspm_ceil_div(M, span);
+    int *work = nullptr;  // [0..34] info, from 40: rows per (block, bin), then first slots per (block, bin)
+    const size_t work_ints = 40 + 2 * (size_t)blocks * kBins;
     cudaError_t err = cudaMalloc(&plan->row_order, sizeof(int) * (size_t)M);
-    if (err == cudaSuccess) err = cudaMalloc(&work, sizeof(int) * 80);
+    if (err == cudaSuccess) err = cudaMalloc(&work, sizeof(int) * work_ints);
     if (err != cudaSuccess) {
         dlspm_cuda_fail(ctx, err, "cudaMalloc(plan)");
         if (plan->row_order) cudaFree(plan->row_order);
         delete plan;
         return DLSPM_ERR_NOMEM;
     }
-    int init[80];
+    int init[40];
     memset(init, 0, sizeof(init));
     init[kBins] = 1;
     int info[kBins + 2];
-    const int blocks = std::max(1, std::min(dlspm_ceil_div(M, 256), ctx->sm_count * 8));
+    int *block_hist = work + 40, *cursor = work + 40 + (size_t)blocks * kBins;
     err = cudaMemcpyAsync(work, init, sizeof(init), cudaMemcpyHostToDevice, st);
     if (err == cudaSuccess) {
-        plan_hist_kernel<<<blocks, 256, 0, st>>>(row_offsets, column_indices, M, work);
-        plan_scan_kernel<<<1, 32, 0, st>>>(work, work + 40);
-        plan_scatter_kernel<<<blocks, 256, 0, st>>>(row_offsets, M, work + 40, plan->row_order);
+        plan_hist_kernel<<<blocks, 256, 0, st>>>(row_offsets, column_indices, M, span, work, block_hist);
+        plan_scan_kernel<<<1, 64, 0, st>>>(block_hist, blocks, work, cursor);
+        plan_scatter_kernel<<<blocks, 256, 0, st>>>(row_offsets, M, span, cursor, plan->row_order);
         err = cudaMemcpyAsync(info, work, sizeof(info), cudaMemcpyDeviceToHost, st);
     }
     if (err == cudaSuccess) err = cudaStreamSynchronize(st);
@@ -536,6 +591,19 @@ extern "C" int dlspm_plan_create(dlspm_ctx *ctx, int M, int K, int nnz, const in
     plan->sorted_rows = info[kBins];
     plan->max_row_len = info[kBins + 1];
     *out = plan;
+    return DLSPM_OK;
+}
+
+extern "C" int dlspm_plan_row_order(const dlspm_plan *plan, int *order, void *stream)
+{
+    if (!plan || (plan->M > 0 && !order)) return DLSPM_ERR_INVALID_ARGUMENT;
+    if (plan->M == 0) return DLSPM_OK;
+    dlspm_ctx *ctx = plan->ctx;
+    int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    DLSPM_CUDA_TRY(ctx, cudaMemcpyAsync(order, plan->row_order, sizeof(int) * (size_t)plan->M, cudaMemcpyDeviceToHost, st));
+    DLSPM_CUDA_TRY(ctx, cudaStreamSynchronize(st));
     return DLSPM_OK;
 }
 

@@ -285,10 +285,31 @@ __global__ void __launch_bounds__(256) batch_analyze_kernel(const BatchProblem *
         }
         __syncthreads();
         if (p.row_order) {
+            // Rows of one length keep their ascending order: the rows are placed chunk by chunk, the
+            // warps of the block one after the other, each row at its rank among the rows of the same
+            // length before it.  (Handing the slots out with atomics gave an order, and kernel times,
+            // that changed from run to run.)
             int *order = const_cast<int *>(p.row_order);
-            for (int r = threadIdx.x; r < p.M; r += blockDim.x) {
-                const int len = p.row_offsets[r + 1] - p.row_offsets[r];
-                order[atomicAdd(&hist[min(max(len, 0), kLenBins - 1)], 1)] = r;
+            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            for (int base = 0; base < p.M; base += blockDim.x) {  // same trip count for the whole block
+                const int r = base + threadIdx.x;
+                const bool have = r < p.M;
+                const int bin = have ? min(max(p.row_offsets[r + 1] - p.row_offsets[r], 0), kLenBins - 1) : 0;
+                const unsigned active = __ballot_sync(0xffffffffu, have);
+                for (int w = 0; w < (int)(blockDim.x >> 5); w++) {
+                    if (warp == w && have) {
+                        const unsigned peers = __match_any_sync(active, bin);
+                        const int leader = __ffs(peers) - 1;
+                        int slot = 0;
+                        if (lane == leader) {
+                            slot = hist[bin];
+                            hist[bin] = slot + __popc(peers);
+                        }
+                        slot = __shfl_sync(peers, slot, leader);
+                        order[slot + __popc(peers & ((1u << lane) - 1u))] = r;
+                    }
+                    __syncthreads();
+                }
             }
         }
         if (threadIdx.x == 0) flags[pi] = s_sorted;

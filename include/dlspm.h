@@ -154,6 +154,12 @@ int dlspm_fused_attention_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz,
 int dlspm_plan_create(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets,
                       const int *column_indices, void *stream, dlspm_plan **plan);
 int dlspm_plan_destroy(dlspm_plan *plan);
+/* Copies the plan's row order (M ints) to HOST memory `order` and synchronises `stream`: rows in
+ * bins by length (bin b: 2^(b-1) <= length < 2^b, empty rows last) from the longest bin to the
+ * shortest, by ascending row number inside a bin.  The order is a function of the pattern alone,
+ * so the kernels that walk it do the same work in the same order in every run.  For inspection
+ * and tests; the SpMM entry points read the plan on the device. */
+int dlspm_plan_row_order(const dlspm_plan *plan, int *order, void *stream);
 
 /* ---- grouped launch over many independent SpMMs ------------------------------------- */
 

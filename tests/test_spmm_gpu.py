@@ -226,6 +226,23 @@ def test_planned_equals_unplanned(pkg, oracle, ctx, dev):
     check(oracle, ro, ci, vals, B, M, N, b)
 
 
+@pytest.mark.parametrize("M", [1, 255, 256, 777, 70001])
+def test_plan_row_order_is_fixed_by_the_pattern(pkg, ctx, dev, M):
+    """Rows come in bins by length (2^(b-1) <= length < 2^b, empty rows last), longest bin first,
+    ascending row numbers inside a bin; nothing about it depends on the run."""
+    K = 700
+    ro, ci = csr_rowlen_normal(pkg, M, K, 0.9, seed=M, cov=1.2)  # wide spread of lengths, empty rows included
+    d_ro, d_ci = to_dev(ro, dev), to_dev(ci, dev)
+    lengths = np.diff(ro)
+    bins = np.where(lengths <= 0, 0, np.floor(np.log2(np.maximum(lengths, 1))).astype(np.int64) + 1)
+    want = np.lexsort((np.arange(M), -bins)).astype(np.int32)  # by bin descending, then by row ascending
+    for _ in range(3):
+        plan = ctx.plan_create(M, K, int(ci.size), d_ro, d_ci)
+        got = plan.row_order()
+        plan.close()
+        assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("offset", [1, 2, 3])
 def test_unaligned_dense_pointers(pkg, oracle, ctx, dev, offset):
     """B and C that do not start on a 16-byte boundary take the narrower vector path."""
