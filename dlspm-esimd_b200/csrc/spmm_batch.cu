@@ -31,18 +31,18 @@ struct BatchProblem {
     int rows_per_tile;  // 8 (one row per warp) or 64 (each warp walks eight rows, served by the coarse launch)
 };
 
-template <int VEC, bool STRICT>
+template <int VEC, bool STRICT, bool PRE>
 __device__ __forceinline__ void batched_tile(const BatchProblem &p, int slab, int row, int start,
-                                             int end, int lane, int2 *stage)
+                                             int end, int lane, int2 *stage, int2 first)
 {
     float *Crow = p.C + (size_t)row * (size_t)p.N;
     const int n0 = slab * 32 * VEC * p.chunks;
     if (p.chunks == 4)
-        spmm_warp_row_slab<VEC, 4, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+        spmm_warp_row_slab<VEC, 4, STRICT, 0, PRE>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage, first);
     else if (p.chunks == 2)
-        spmm_warp_row_slab<VEC, 2, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+        spmm_warp_row_slab<VEC, 2, STRICT, 0, PRE>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage, first);
     else
-        spmm_warp_row_slab<VEC, 1, STRICT>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage);
+        spmm_warp_row_slab<VEC, 1, STRICT, 0, PRE>(p.values, p.cols, start, end, p.B, Crow, p.N, n0, lane, stage, first);
 }
 
 // Warps (= rows of a fine tile) per thread block of the grouped launch.
@@ -57,9 +57,53 @@ __device__ __forceinline__ void batched_row(const BatchProblem &p, int slab, int
 {
     const int row = p.row_order ? __ldg(p.row_order + slot) : slot;
     const int start = __ldg(p.row_offsets + row), end = __ldg(p.row_offsets + row + 1);
-    if (p.vec == 4) batched_tile<4, STRICT>(p, slab, row, start, end, lane, stage);
-    else if (p.vec == 2) batched_tile<2, STRICT>(p, slab, row, start, end, lane, stage);
-    else batched_tile<1, STRICT>(p, slab, row, start, end, lane, stage);
+    const int2 none = make_int2(0, 0);
+    if (p.vec == 4) batched_tile<4, STRICT, false>(p, slab, row, start, end, lane, stage, none);
+    else if (p.vec == 2) batched_tile<2, STRICT, false>(p, slab, row, start, end, lane, stage, none);
+    else batched_tile<1, STRICT, false>(p, slab, row, start, end, lane, stage, none);
+}
+
+// The rows first + warp, first + warp + 8, ... (below `last`) of a coarse tile, walked by one warp.
+// Rows of such tiles hold a handful of nonzeros, so a row on its own is a chain of four dependent
+// loads (row number, offsets, pairs, rows of B) in front of very little arithmetic.  Here lane i
+// fetches the number and the offsets of the warp's i-th row (one chain for all eight rows), and the
+// pairs of the next row are asked for before the current row is computed, so that a row waits for its
+// gathers from B only.
+template <bool STRICT>
+__device__ __forceinline__ void batched_rows_coarse(const BatchProblem &p, int slab, int first, int last, int warp,
+                                                    int lane, int2 *stage)
+{
+    constexpr int kRows = kCoarseRows / kBatchWarps;
+    static_assert(kRows <= 32, "one lane per row of the warp");
+    int my_row = -1, my_start = 0, my_end = 0;
+    {
+        const int slot = first + warp + kBatchWarps * lane;
+        if (lane < kRows && slot < last) {
+            my_row = p.row_order ? __ldg(p.row_order + slot) : slot;
+            my_start = __ldg(p.row_offsets + my_row);
+            my_end = __ldg(p.row_offsets + my_row + 1);
+        }
+    }
+    int row = __shfl_sync(0xffffffffu, my_row, 0);
+    int start = __shfl_sync(0xffffffffu, my_start, 0), end = __shfl_sync(0xffffffffu, my_end, 0);
+    int2 pairs = make_int2(0, 0);
+    if (row >= 0) pairs = spmm_first_pairs(p.values, p.cols, start, end, lane);
+#pragma unroll 1
+    for (int i = 0; i < kRows && row >= 0; i++) {
+        const int nxt = min(i + 1, kRows - 1);
+        int nrow = __shfl_sync(0xffffffffu, my_row, nxt);
+        const int nstart = __shfl_sync(0xffffffffu, my_start, nxt), nend = __shfl_sync(0xffffffffu, my_end, nxt);
+        if (i + 1 >= kRows) nrow = -1;
+        int2 npairs = make_int2(0, 0);
+        if (nrow >= 0) npairs = spmm_first_pairs(p.values, p.cols, nstart, nend, lane);
+        if (p.vec == 4) batched_tile<4, STRICT, true>(p, slab, row, start, end, lane, stage, pairs);
+        else if (p.vec == 2) batched_tile<2, STRICT, true>(p, slab, row, start, end, lane, stage, pairs);
+        else batched_tile<1, STRICT, true>(p, slab, row, start, end, lane, stage, pairs);
+        row = nrow;
+        start = nstart;
+        end = nend;
+        pairs = npairs;
+    }
 }
 
 // Persistent thread blocks pull tile numbers from a device counter.  tile_start[i] is the first
@@ -94,8 +138,7 @@ spmm_batched_kernel(const BatchProblem *__restrict__ problems, const long long *
         if constexpr (COARSE) {
             const int first = (int)(t - (long long)slab * p.row_groups) * kCoarseRows;
             const int last = min(first + kCoarseRows, p.M);
-#pragma unroll 1
-            for (int slot = first + warp; slot < last; slot += kBatchWarps) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
+            batched_rows_coarse<STRICT>(p, slab, first, last, warp, lane, stage[warp]);
         } else {
             const int slot = (int)(t - (long long)slab * p.row_groups) * kBatchWarps + warp;
             if (slot < p.M) batched_row<STRICT>(p, slab, slot, lane, stage[warp]);
@@ -120,8 +163,11 @@ inline int rows_per_tile_for(const dlspm_problem &q, bool allow_coarse)
 
 // (One-chunk slabs for such problems, so that the slab of B would stay in L1 for the 64 rows of a
 // tile, were measured and lost: 0.87 -> 0.50 of the HBM rate on 64 x 64 at 2 %, N = 1024.)
-// Coarse tiles are used only when the batch still yields several tiles per resident thread block
-// with them; a small batch keeps the finest tiling so that it fills the device.
+// Coarse tiles are used only when the batch still yields about four of them per SM; a smaller batch
+// keeps the finest tiling so that it fills the device.  (Measured with batches of one shape, as a
+// fraction of the HBM copy rate, fine / coarse tiles: 1894 problems of 64 x 64 at 10 %, N = 1024
+// 0.46 / 0.58; 311 problems of 64 x 64 at 2 %, N = 3136 0.56 / 0.77; 476 of 64 x 64 at 2 %, N = 1024
+// 0.47 / 0.66; below four tiles per SM coarse tiles lose as often as they win.)
 bool coarse_tiles_pay(const dlspm_ctx *ctx, int count, const dlspm_problem *problems)
 {
     long long tiles = 0;
@@ -132,7 +178,7 @@ bool coarse_tiles_pay(const dlspm_ctx *ctx, int count, const dlspm_problem *prob
         const int slabs = dlspm_ceil_div(q.N, 32 * vec * spmm_slab_chunks(q.N, vec));
         tiles += (long long)dlspm_ceil_div(q.M, rows_per_tile_for(q, true)) * slabs;
     }
-    return tiles >= 4LL * 8 * ctx->sm_count;
+    return tiles >= 4LL * ctx->sm_count;
 }
 
 // Table entry of one problem (natural row order).

@@ -113,12 +113,24 @@ __device__ __forceinline__ void spmm_accumulate_staged(const int2 *stage, int cn
 template <int U>
 constexpr int kLoneBatch = U == 1 ? 8 : U == 2 ? 4 : 0;
 
-// stage: 32 int2 slots private to this warp.
-template <int VEC, int U, bool STRICT, int J = 0>
+// The (column, value) pair of nonzero start + lane of a row, (0, 0) beyond its end: what the first
+// staging step of spmm_warp_row_slab loads.  A caller that walks several rows can ask for the next
+// row's pairs before it computes the current row and hand them over (PRE = true), which takes that
+// load out of the next row's chain of dependent latencies.
+__device__ __forceinline__ int2 spmm_first_pairs(const float *__restrict__ values, const int *__restrict__ cols,
+                                                 int start, int end, int lane)
+{
+    const int p = start + lane;
+    return p < end ? make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p))) : make_int2(0, 0);
+}
+
+// stage: 32 int2 slots private to this warp.  PRE: `first` holds spmm_first_pairs of this row.
+template <int VEC, int U, bool STRICT, int J = 0, bool PRE = false>
 __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
                                                    const int *__restrict__ cols, int start, int end,
                                                    const float *__restrict__ B, float *__restrict__ Crow,
-                                                   int N, int n0, int lane, int2 *stage)
+                                                   int N, int n0, int lane, int2 *stage,
+                                                   int2 first = make_int2(0, 0))
 {
     float acc[U][VEC];
     int cidx[U];
@@ -132,7 +144,8 @@ __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ val
     for (int base = start; base < end; base += 32) {
         const int p = base + lane;
         int2 cv = make_int2(0, 0);
-        if (p < end) cv = make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p)));
+        if (PRE && base == start) cv = first;
+        else if (p < end) cv = make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p)));
         stage[lane] = cv;
         __syncwarp();
         spmm_accumulate_staged<VEC, U, STRICT, J>(stage, min(32, end - base), B, N, cidx, acc);
