@@ -196,6 +196,14 @@ BatchProblem make_batch_problem(const dlspm_problem &q, bool allow_coarse)
     b.row_groups = dlspm_ceil_div(q.M, b.rows_per_tile);
     b.vec = dlspm_vec_width(q.N, q.B, q.C);
     b.chunks = spmm_slab_chunks(q.N, b.vec);
+    // Coarse tiles whose rows of B are gathered several times over (nnz / K times on average): with
+    // slabs of 512 columns the slabs of B under the resident tiles (plus the C they write) exceed L2
+    // and B is fetched from DRAM 1.4 to 1.6 times (ncu); slabs of 256 columns halve that footprint.
+    // Measured as a fraction of the HBM copy rate, 512 / 256 / 128 columns: 64 x 64 at 10 %, N = 1024
+    // 0.61 / 0.63 / 0.39; 256 x 256 at 2 %, N = 3136 0.59 / 0.63 / 0.37; 256 x 256 at 5 %, N = 1024
+    // 0.35 / 0.43 / 0.24.  Without that reuse the narrower slab only doubles the row visits
+    // (64 x 64 at 2 %: 0.94 -> 0.84), so those keep the wide slab.
+    if (b.rows_per_tile > kBatchWarps && b.chunks > 2 && (double)q.nnz >= 3.0 * (double)q.K) b.chunks = 2;
     b.K = q.K;
     b.row_order = nullptr;
     b.nnz = q.nnz;

@@ -42,6 +42,25 @@ __device__ __forceinline__ void store_vec(float *__restrict__ p, const float (&v
     }
 }
 
+// The same store marked as streaming (evicted from L2 first): for output that is written once and
+// not read again by the kernel, so that it does not push the rows of B that are still needed out
+// of L2.
+template <int VEC>
+__device__ __forceinline__ void store_vec_streaming(float *__restrict__ p, const float (&v)[VEC])
+{
+#ifdef DLSPM_NO_STREAMING_STORES
+    store_vec<VEC>(p, v);
+#else
+    if constexpr (VEC == 4) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+    } else if constexpr (VEC == 2) {
+        __stcs(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]));
+    } else {
+        __stcs(p, v[0]);
+    }
+#endif
+}
+
 template <bool STRICT>
 __device__ __forceinline__ float mad(float a, float b, float c)
 {
@@ -153,7 +172,7 @@ __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ val
     }
 #pragma unroll
     for (int u = 0; u < U; u++) {
-        if (cidx[u] < N) store_vec<VEC>(Crow + cidx[u], acc[u]);
+        if (cidx[u] < N) store_vec_streaming<VEC>(Crow + cidx[u], acc[u]);
     }
 }
 
