@@ -52,8 +52,15 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
         const int p = base + lane;
         const int col = col_next;
         col_next = p + stride < end ? __ldg(cols + p + stride) : -1;
-        const float r = sddmm_pass<G, R, KSPLIT>(a, rhs4, chunks, col, g, t, kmask, ksub);
-        if (p < end && (!KSPLIT || (t & kmask) == ksub)) out[p] = mask ? __ldg(mask + p) * r : r;
+        if constexpr (KSPLIT) {
+            const float r = sddmm_pass<G, R, true>(a, rhs4, chunks, col, g, t, kmask, ksub);
+            if (p < end && (t & kmask) == ksub) out[p] = mask ? __ldg(mask + p) * r : r;
+        } else {
+            // nonzeros dealt to the lane groups in turn: this lane ends up with nonzero `q` of the row
+            const float r = sddmm_pass_dealt<G, R>(a, rhs4, chunks, col, g, t);
+            const int q = base + sddmm_dealt_slot(G, g, t);
+            if (q < end) out[q] = mask ? __ldg(mask + q) * r : r;
+        }
     }
 }
 

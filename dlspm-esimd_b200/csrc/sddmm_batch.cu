@@ -56,8 +56,9 @@ __device__ __forceinline__ void sddmm_one_row(const RowProblem &p, int row, int 
         const int q = base + lane;
         const int col = col_next;
         col_next = q + stride < end ? __ldg(p.cols + q + stride) : -1;
-        const float r = sddmm_pass<G, R>(a, rhs4, p.chunks, col, g, t);
-        if (q < end) p.out[q] = p.mask ? __ldg(p.mask + q) * r : r;
+        const float r = sddmm_pass_dealt<G, R>(a, rhs4, p.chunks, col, g, t);
+        const int o = base + sddmm_dealt_slot(G, g, t);  // the nonzero whose dot product this lane holds
+        if (o < end) p.out[o] = p.mask ? __ldg(p.mask + o) * r : r;
     }
 }
 

@@ -95,6 +95,39 @@ __device__ __forceinline__ float sddmm_pass(const float4 (&a)[R], const float4 *
     return part[0];
 }
 
+// The same pass with the nonzeros DEALT to the groups in turn: nonzero i of the pass (its column on
+// lane i, -1 past the end of the row) goes to group i % (32/G) as that group's (i / (32/G))-th.  In a
+// pass with few nonzeros (the last pass of every row, the only pass of a short row) every group then
+// has work in the first ceil(cnt / (32/G)) steps only and the remaining steps are skipped by all
+// lanes, where with blocks of G the first group worked through min(cnt, G) nonzeros alone.
+// Returns, on lane g*G + t, the dot product of nonzero sddmm_dealt_slot(G, g, t) of the pass.  Every
+// dot product is summed in the same order as in sddmm_pass, so the two give the same bits.
+template <int G, int R>
+__device__ __forceinline__ float sddmm_pass_dealt(const float4 (&a)[R], const float4 *__restrict__ rhs4,
+                                                  int chunks, int col, int g, int t)
+{
+    constexpr int NG = 32 / G;
+    float part[G];
+#pragma unroll
+    for (int k = 0; k < G; k++) {
+        const int c = __shfl_sync(0xffffffffu, col, k * NG + g);
+        float acc = 0.f;
+        if (c >= 0) {
+            const float4 *brow = rhs4 + (size_t)c * (size_t)chunks;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int idx = r * G + t;
+                if (idx < chunks) acc = dot4(a[r], __ldg(brow + idx), acc);
+            }
+        }
+        part[k] = acc;
+    }
+    group_transpose_reduce<G>(part, t);
+    return part[0];
+}
+
+__device__ __forceinline__ int sddmm_dealt_slot(int G, int g, int t) { return t * (32 / G) + g; }
+
 // Group width and chunks per lane for a row of `chunks` float4: G*R >= chunks with G >= 8.
 // Returns false when the row is too long for the register-resident path.
 __host__ __device__ inline bool sddmm_layout(int chunks, int *G, int *R)
