@@ -41,15 +41,18 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
         const int p = base + lane;
         const int col = col_next;
         col_next = p + stride < end ? __ldg(cols + p + stride) : -1;
-        float score = sddmm_pass<G, R>(q, b4, chunks, col, g, t);
+        // nonzeros dealt to the lane groups in turn (see sddmm_pass_dealt): this lane's score belongs
+        // to nonzero base + sddmm_dealt_slot of the row, whose column sits on lane sddmm_dealt_slot
+        float score = sddmm_pass_dealt<G, R>(q, b4, chunks, col, g, t);
         if constexpr (MODE == kScaled) score *= scale;
         if constexpr (MODE == kSoftmax) {
             // streaming softmax: weights relative to the running maximum; the partial row and the
             // running sum are rescaled when the maximum grows
-            const float x = col >= 0 ? score * scale : -INFINITY;
+            const bool stored = base + sddmm_dealt_slot(G, g, t) < end;
+            const float x = stored ? score * scale : -INFINITY;
             const float m_new = fmaxf(run_max, warp_max(x));  // finite: a pass has a stored entry
             const float corr = expf(run_max - m_new);         // 0 on the first pass
-            score = col >= 0 ? expf(x - m_new) : 0.f;
+            score = stored ? expf(x - m_new) : 0.f;
             run_sum = run_sum * corr + warp_sum(score);
             run_max = m_new;
 #pragma unroll
@@ -62,9 +65,8 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
         }
 #pragma unroll
         for (int k = 0; k < G; k++) {
-            const int src = g * G + k;
-            const int cc = __shfl_sync(0xffffffffu, col, src);
-            const float s = __shfl_sync(0xffffffffu, score, src);
+            const int cc = __shfl_sync(0xffffffffu, col, k * (32 / G) + g);  // the group's k-th nonzero
+            const float s = __shfl_sync(0xffffffffu, score, g * G + k);
             if (cc >= 0) {
                 const float4 *drow = d4 + (size_t)cc * (size_t)chunks;
 #pragma unroll
