@@ -151,7 +151,15 @@ sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
 // warp loads the lhs row, shorter runs per warp).  Returns the shift with the least estimated time.
 inline int sddmm_wave_shift(long long blocks, long long resident, double avg_row)
 {
-    if (blocks <= resident || blocks > 8 * resident) return 0;
+    if (blocks <= resident) {
+        // Less than one wave (4096 rows with N = 32 are 512 blocks for 1184 resident ones): the device
+        // is partly empty and the launch lasts as long as one warp needs for its row, so rows are
+        // shared while the launch still fits in one wave and a warp keeps more than one pass.
+        int s = 0;
+        while (s < 2 && (blocks << (s + 1)) <= resident && avg_row > 64.0 * (1 << s)) s++;
+        return s;
+    }
+    if (blocks > 8 * resident) return 0;
     int best = 0;
     double best_cost = 1e30;
     for (int s = 0; s <= 2 && avg_row > 32.0 * (1 << s); s++) {
