@@ -9,7 +9,7 @@
 
 // staging slots of the pipelined host-buffer calls (copy in, launch, copy out overlap across slots)
 constexpr int kPipeSlots = 4;
-constexpr int kSideStreams = 9;
+constexpr int kSideStreams = 11;
 
 struct dlspm_ctx {
     int device;

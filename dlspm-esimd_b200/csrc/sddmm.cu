@@ -264,6 +264,18 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         const int chunks = N / 4;
         const int shift = sddmm_split_shift(ctx, M, nnz);
         const int kshift = sddmm_k_shift(ctx, M, nnz, shift, 16.0);
+        const double avg_row = (double)nnz / (double)M;
+#ifndef DLSPM_NO_NARROW_GROUPS
+        // Rows of up to 32 floats: groups of 4 lanes (8 nonzeros in flight per step instead of 4, a
+        // butterfly of 3 shuffles instead of 7).  Warps that share the nonzeros inside a pass select
+        // by the index within a group, so at most 4 warps can do that with groups of 4.
+        if (chunks <= 8 && kshift <= 2) {
+            if (chunks <= 4) launch_fast<4, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, avg_row);
+            else launch_fast<4, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, avg_row);
+            DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+            return DLSPM_OK;
+        }
+#endif
         if (G == 8 && R == 1) launch_fast<8, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
         else if (G == 8 && R == 2) launch_fast<8, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);
         else if (G == 8 && R == 4) launch_fast<8, 4>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, (double)nnz / (double)M);

@@ -8,7 +8,7 @@
 // counter (thread blocks pull tiles of eight where the fused chain shares rows between warps), one
 // warp per row, and every row is processed exactly as in the
 // single-matrix kernels (same passes, same butterfly, same order of additions), so results have the
-// same bits.  A batch with one inner dimension is one launch; a mixed batch is at most six.
+// same bits.  A batch with one inner dimension is one launch; a mixed batch is at most twelve.
 #include <algorithm>
 #include <vector>
 
@@ -21,8 +21,9 @@ using namespace dlspm;
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kClasses = 10;  // the six (G, R) layouts of sddmm_layout, then SDDMM rows beyond 1024 floats in segments of
-                              // 1024 / 512 floats, one warp per row (6, 7) or rows shared between warps (8, 9)
+constexpr int kClasses = 12;  // the six (G, R) layouts of sddmm_layout (0..5), then SDDMM rows beyond 1024 floats in segments
+                              // of 1024 / 512 floats, one warp per row (6, 7) or rows shared between warps (8, 9), then
+                              // SDDMM rows of up to 16 / 32 floats in groups of four lanes (10, 11)
 constexpr int kOpSddmm = 0, kOpFused = 1, kOpSddmmLong = 2, kOpSddmmLongShared = 3;
 
 struct RowProblem {
@@ -246,7 +247,9 @@ int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, cons
     case 6: return launch_class<32, 8, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     case 7: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     case 8: return launch_class<32, 8, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
-    default: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 9: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 10: return launch_class<4, 1, kOpSddmm>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    default: return launch_class<4, 2, kOpSddmm>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     }
 }
 
@@ -272,14 +275,15 @@ struct HostEntry {
 // Classes with too few rows to fill the device with one warp per row: rows are shared between 2, 4 or
 // 8 warps, as the single-matrix launchers do for lone patterns (SDDMM: the outputs of different
 // nonzeros are independent, nothing is combined; fused chain: partial rows are added through shared
-// memory).  Register-resident rows (classes 0..5) deal out
+// memory).  Register-resident rows (classes 0..5, 10, 11) deal out
 // the passes of 32 nonzeros, as long as a warp keeps about one pass; rows beyond 1024 floats (classes
 // 6, 7) deal out the nonzeros inside every pass and move to the classes 8, 9, whose kernels carry the
 // extra test.
 void choose_sharing(const dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kClasses])
 {
     const long long want = (long long)ctx->sm_count * 32;
-    for (int c = 0; c < 8; c++) {
+    for (int c = 0; c < kClasses; c++) {
+        if (c == 8 || c == 9) continue;  // filled below from 6 and 7
         std::vector<HostEntry> &v = by_class[c];
         long long rows = 0;
         for (const HostEntry &e : v) rows += e.p.M;
@@ -288,14 +292,14 @@ void choose_sharing(const dlspm_ctx *ctx, std::vector<HostEntry> (&by_class)[kCl
         while (cls_shift < 3 && (rows << cls_shift) < want) cls_shift++;
         for (HostEntry &e : v) {
             int s = 0;
-            if (c < 6) {
+            if (c < 6 || c >= 10) {
                 while (s < cls_shift && e.avg_row > 32.0 * (1 << s)) s++;
             } else {
                 s = cls_shift;
             }
             e.p.shift = s;
         }
-        if (c >= 6) {  // shared long rows run on the kernels with the extra test
+        if (c == 6 || c == 7) {  // shared long rows run on the kernels with the extra test
             for (HostEntry &e : v)
                 if (e.p.shift > 0) by_class[c + 2].push_back(e);
             v.erase(std::remove_if(v.begin(), v.end(), [](const HostEntry &e) { return e.p.shift > 0; }), v.end());
@@ -437,7 +441,8 @@ int dlspm_sddmm_batched_at(dlspm_ctx *ctx, int count, const dlspm_sddmm_problem 
             e.index = i;
             // beyond the register-resident layouts: segments of 1024 floats, of 512 from N = 2052 on
             // (the choice of the single-matrix launcher)
-            const int cls = sddmm_layout(q.N / 4, &G, &R) ? layout_class(G, R) : (q.N > 2048 ? 7 : 6);
+            // rows of up to 32 floats: groups of four lanes, as in the single-matrix launcher
+            const int cls = q.N <= 16 ? 10 : q.N <= 32 ? 11 : sddmm_layout(q.N / 4, &G, &R) ? layout_class(G, R) : (q.N > 2048 ? 7 : 6);
             by_class[cls].push_back(e);
         } else {
             int rc = dlspm_sddmm_csr_masked_f32(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices, q.mask_values,

@@ -220,7 +220,7 @@ typedef struct dlspm_fused_problem {
 } dlspm_fused_problem;
 
 /* Runs `count` independent SDDMMs (each as dlspm_sddmm_csr_masked_f32 would) in one persistent
- * launch per register layout present in the batch (the layout follows from N: at most ten, one for
+ * launch per register layout present in the batch (the layout follows from N: at most twelve, one for
  * a batch with a single inner dimension).  Replaces the per-matrix process launches of
  * SDDMM/batch-run-sddmm_fromfile:31-47, where every layer-sized pattern is launch-bound on its own.
  * `problems` is a HOST array; the tables go to the context's scratch, so the same rules as for
