@@ -23,7 +23,7 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kClasses = 12;  // the six (G, R) layouts of sddmm_layout (0..5), then SDDMM rows beyond 1024 floats in segments
                               // of 1024 / 512 floats, one warp per row (6, 7) or rows shared between warps (8, 9), then
-                              // SDDMM rows of up to 16 / 32 floats in groups of four lanes (10, 11)
+                              // rows of up to 16 / 32 floats in groups of four lanes (10, 11)
 constexpr int kOpSddmm = 0, kOpFused = 1, kOpSddmmLong = 2, kOpSddmmLongShared = 3;
 
 struct RowProblem {
@@ -248,8 +248,8 @@ int launch_class_by_index(dlspm_ctx *ctx, int cls, const RowProblem *d_tab, cons
     case 7: return launch_class<32, 4, kOpSddmmLong>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     case 8: return launch_class<32, 8, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     case 9: return launch_class<32, 4, kOpSddmmLongShared>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
-    case 10: return launch_class<4, 1, kOpSddmm>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
-    default: return launch_class<4, 2, kOpSddmm>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    case 10: return launch_class<4, 1, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
+    default: return launch_class<4, 2, OP>(ctx, d_tab, d_starts, count, tiles, d_counter, shared, st);
     }
 }
 
@@ -474,14 +474,14 @@ int dlspm_fused_batched_at(dlspm_ctx *ctx, int count, const dlspm_fused_problem 
             e.avg_row = (double)q.nnz / (double)q.M;
             e.work = (double)q.nnz * q.N + (double)q.M;  // rows without entries still cost a store
             e.index = i;
-            by_class[layout_class(G, R)].push_back(e);
+            by_class[q.N <= 16 ? 10 : q.N <= 32 ? 11 : layout_class(G, R)].push_back(e);
         } else {
             int rc = dlspm_fused_sddmm_spmm_f32(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices, q.C, q.B, q.D,
                                                 q.E, st);
             if (rc) return rc;
         }
     }
-    choose_sharing(ctx, by_class);  // classes 6..9 are never filled for the fused chain
+    choose_sharing(ctx, by_class);  // the classes 6..9 are never filled for the fused chain
     return rows_batched_at<kOpFused>(ctx, by_class, tables, pinned, st);
 }
 

@@ -12,8 +12,7 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [(8, 8), (61, 83), (64, 256), (256, 64), (300, 512)]
 SPARSITIES = [0.5, 0.7, 0.8, 0.9, 0.95, 0.98]
-# one inner dimension per layout (4x1, 4x2 for SDDMM / 8x1 for the fused chain, 8x2, 8x4, 16x4, 32x4, 32x8), scalar
-# fall-backs, long rows in segments
+# one inner dimension per layout (4x1, 4x2, 8x2, 8x4, 16x4, 32x4, 32x8), scalar fall-backs, long rows in segments
 WIDTHS = [16, 32, 64, 128, 256, 512, 1024, 100, 50, 33, 1028, 3136, 8, 24]
 
 
