@@ -158,6 +158,62 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_subwarp_kernel(const S
         *reinterpret_cast<float4 *>(a.C + (size_t)row * (size_t)a.N + t * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
 }
 
+// The same narrow operand with too few rows for a row per lane group: the 32/LANES groups of a warp
+// share ONE row.  The warp fetches 32 (column, value) pairs per step and deals them to the groups in
+// turn (pair i to group i mod 32/LANES), every group gathers the B rows of its pairs with all its
+// lanes busy, and the groups' partial rows are added with shuffles at the end (fixed order, but not
+// CSR order: not used in strict mode).  A full warp per row with one 128-column chunk would leave
+// 24 of 32 lanes idle at N = 32.
+template <int LANES>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) spmm_subwarp_shared_kernel(const SpmmArgs a)
+{
+    constexpr int kGroups = 32 / LANES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane / LANES, t = lane % LANES;
+    const int slot = blockIdx.x * kWarpsPerCta + warp;
+    if (slot >= a.M) return;
+    const int row = a.row_order ? a.row_order[slot] : slot;
+    const int start = __ldg(a.row_offsets + row), len = __ldg(a.row_offsets + row + 1) - start;
+    const bool active = t * 4 < a.N;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float *bcol = a.B + t * 4;
+    for (int base = 0; base < len; base += 32) {
+        int c = 0;
+        float v = 0.f;
+        if (base + lane < len) {
+            c = __ldg(a.cols + start + base + lane);
+            v = __ldg(a.values + start + base + lane);
+        }
+#pragma unroll
+        for (int j = 0; j < LANES; j++) {
+            if (base + j * kGroups >= len) break;  // uniform over the warp
+            const int src = j * kGroups + g;       // this group's j-th pair of the step
+            const int cj = __shfl_sync(0xffffffffu, c, src);
+            const float vj = __shfl_sync(0xffffffffu, v, src);
+            if (active && base + src < len) {
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(bcol + (size_t)cj * (size_t)a.N));
+                acc[0] = fmaf(vj, b.x, acc[0]);
+                acc[1] = fmaf(vj, b.y, acc[1]);
+                acc[2] = fmaf(vj, b.z, acc[2]);
+                acc[3] = fmaf(vj, b.w, acc[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int s = LANES; s < 32; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], s);
+    }
+    if (active && g == 0)
+        *reinterpret_cast<float4 *>(a.C + (size_t)row * (size_t)a.N + t * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+template <int LANES>
+void launch_subwarp_shared(const SpmmArgs &a, cudaStream_t st)
+{
+    spmm_subwarp_shared_kernel<LANES><<<(unsigned)dlspm_ceil_div(a.M, kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(a);
+}
+
 template <int LANES>
 void launch_subwarp(const SpmmArgs &a, bool strict, cudaStream_t st)
 {
@@ -249,6 +305,22 @@ int spmm_launch(dlspm_ctx *ctx, int M, int N, int nnz, const float *values, cons
         split = 8;
     // narrow N: several rows per warp, but never so many that the matrix yields too few warps
     int lanes = 32;
+    if (vec == 4 && N <= 64 && !strict) {
+        // Too few rows for a row per lane group (fewer than 16 warps per SM that way), enough for a
+        // row per warp: the groups share the row.  Measured at N = 32 and 30 % nonzeros, GFLOP/s:
+        // 4096 x 1024 2019 -> 3687, 8192 x 2048 3856 -> 6312, 4096 x 4096 2668 -> 4971, 8192 x 8192
+        // 3610 -> 5651; with fewer rows than 16 per SM the launch gets too few warps either way and
+        // the warps-per-row split below does better (1024 x 1024 1016 -> 844: left alone).
+        const int narrow = N <= 16 ? 4 : N <= 32 ? 8 : 16;
+        if ((long long)M * narrow / 32 < (long long)ctx->sm_count * 16 && (long long)M >= (long long)ctx->sm_count * 16 &&
+            mean_len >= 16.0) {
+            if (narrow == 4) launch_subwarp_shared<4>(a, st);
+            else if (narrow == 8) launch_subwarp_shared<8>(a, st);
+            else launch_subwarp_shared<16>(a, st);
+            DLSPM_CUDA_TRY(ctx, cudaGetLastError());
+            return DLSPM_OK;
+        }
+    }
     if (vec == 4 && N <= 64 && split == 1) {
         lanes = N <= 16 ? 4 : N <= 32 ? 8 : 16;
         while (lanes < 32 && (long long)M * lanes / 32 < (long long)ctx->sm_count * 16) lanes *= 2;

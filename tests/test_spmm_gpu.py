@@ -128,6 +128,30 @@ def test_narrow_dense_operand_many_rows(pkg, oracle, ctx, dev, N):
         assert np.array_equal(strict.view(np.uint32), oracle.spmm(vals, ro, ci, B, M, N).view(np.uint32))
 
 
+@pytest.mark.parametrize("M,N", [(3000, 32), (4096, 28), (6000, 16), (2500, 64), (4500, 8), (3000, 36)])
+def test_narrow_dense_operand_lane_groups_share_a_row(pkg, oracle, ctx, dev, M, N):
+    """Narrow N with too few rows for a row per lane group: the groups of a warp share the row (its
+    pairs dealt to them in turn, partial rows added at the end).  Empty rows, rows shorter than the
+    number of groups and rows of several fetch rounds; with and without a plan."""
+    K = 400
+    seed = 700 + N
+    ro, ci = csr_rowlen_normal(pkg, M, K, 0.85, seed, cov=0.9)
+    lengths = np.diff(ro)
+    assert (lengths == 0).any() and (lengths < 4).any() and lengths.max() > 64
+    vals = pkg.gen_dense_host(int(ci.size), seed, 2)
+    B = dense(pkg, K, N, seed, 10)
+    out = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+    check(oracle, ro, ci, vals, B, M, N, out)
+    planned = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B, plan=True)
+    assert np.array_equal(out.view(np.uint32), planned.view(np.uint32))
+    ctx.set_option(pkg.OPT_STRICT_FP32, 1)  # strict mode keeps the CSR order (another kernel)
+    try:
+        strict = run_spmm(ctx, dev, M, K, N, ro, ci, vals, B)
+    finally:
+        ctx.set_option(pkg.OPT_STRICT_FP32, 0)
+    assert np.array_equal(strict.view(np.uint32), oracle.spmm(vals, ro, ci, B, M, N).view(np.uint32))
+
+
 def test_few_long_rows_shared_between_warps(pkg, oracle, ctx, dev):
     """Few rows with many nonzeros: 2, 4 or 8 warps share a row; strict mode keeps one warp per row."""
     for (M, K, N) in [(64, 4096, 256), (300, 2048, 132), (1024, 4096, 260), (9, 3000, 1024)]:
