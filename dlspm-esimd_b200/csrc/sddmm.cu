@@ -145,6 +145,73 @@ sddmm_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
     }
 }
 
+// Rows that rule out 128-bit loads (N not a multiple of 4, or unaligned operands) up to 256 floats:
+// the group layout of the fast path with scalar elements.  Lane t of a group of G lanes owns the
+// elements e*G + t (e = 0..E-1) of a dense row, so a group reads G consecutive floats per load; the
+// lhs row stays in registers, the nonzeros of a pass are dealt to the groups in turn and the
+// transposing butterfly finishes G dot products with G-1 shuffles per lane.  The any-width kernel
+// above re-reads the lhs row and runs a full-warp reduction (five shuffles) for every nonzero; at
+// N = 49, a width of the data set's own table, that is three times the instructions.
+template <int G, int E>
+__global__ void __launch_bounds__(kWarps * 32)
+sddmm_rows_scalar_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                         const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
+                         int M, int N, const float *__restrict__ mask, int split_shift)
+{
+    constexpr int NG = 32 / G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // 1 << split_shift warps share a row and take its passes in turn (patterns with few rows)
+    const int slot = blockIdx.x * kWarps + warp;
+    const int row = slot >> split_shift;
+    if (row >= M) return;
+    const int g = lane / G, t = lane % G;
+    const int stride = 32 << split_shift;
+    const int start = __ldg(row_offsets + row) + 32 * (slot & ((1 << split_shift) - 1));
+    const int end = __ldg(row_offsets + row + 1);
+    if (start >= end) return;
+    const float *arow = lhs + (size_t)row * (size_t)N;
+    float a[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+        const int idx = e * G + t;
+        a[e] = idx < N ? __ldg(arow + idx) : 0.f;
+    }
+    int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
+    for (int base = start; base < end; base += stride) {
+        const int col = col_next;
+        col_next = base + stride + lane < end ? __ldg(cols + base + stride + lane) : -1;
+        float part[G];
+#pragma unroll
+        for (int k = 0; k < G; k++) {
+            const int c = __shfl_sync(0xffffffffu, col, k * NG + g);
+            float acc = 0.f;
+            if (c >= 0) {
+                const float *brow = rhs + (size_t)c * (size_t)N;
+#pragma unroll
+                for (int e = 0; e < E; e++) {
+                    const int idx = e * G + t;
+                    if (idx < N) acc = fmaf(a[e], __ldg(brow + idx), acc);
+                }
+            }
+            part[k] = acc;
+        }
+        group_transpose_reduce<G>(part, t);
+        const int q = base + sddmm_dealt_slot(G, g, t);
+        if (q < end) out[q] = mask ? __ldg(mask + q) * part[0] : part[0];
+    }
+}
+
+template <int G>
+void launch_scalar(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M, int N,
+                   const float *mask, int split_shift, cudaStream_t st)
+{
+    const unsigned blocks = (unsigned)((((long long)M << split_shift) + kWarps - 1) / kWarps);
+    const int per_lane = dlspm_ceil_div(N, G);
+    if (per_lane <= 2) sddmm_rows_scalar_kernel<G, 2><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, N, mask, split_shift);
+    else if (per_lane <= 4) sddmm_rows_scalar_kernel<G, 4><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, N, mask, split_shift);
+    else sddmm_rows_scalar_kernel<G, 8><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, N, mask, split_shift);
+}
+
 // Patterns of one to a few waves of thread blocks: the last wave is often nearly empty (6144 rows are
 // 768 blocks for 592 resident ones, i.e. two waves for 1.3 waves of work).  Two or four warps per
 // row make the blocks shorter and the waves finer; a shared row costs about 8 % per doubling (every
@@ -291,6 +358,11 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         else if (N > 2048) sddmm_rows_long_kernel<4, false><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, 0);
         else if (kshift > 0) sddmm_rows_long_kernel<8, true><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, kshift);
         else sddmm_rows_long_kernel<8, false><<<lblocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N / 4, mask, 0);
+    } else if (N <= 256) {  // no 128-bit loads: the group layout with scalar elements
+        const int shift = sddmm_split_shift(ctx, M, nnz);
+        if (N <= 64) launch_scalar<8>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask, shift, st);
+        else if (N <= 128) launch_scalar<16>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask, shift, st);
+        else launch_scalar<32>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask, shift, st);
     } else if (vec == 2) {
         sddmm_generic_kernel<2><<<blocks, kWarps * 32, 0, st>>>(row_offsets, column_indices, lhs, rhs, out_values, M, N, mask);
     } else {

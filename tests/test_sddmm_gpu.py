@@ -194,7 +194,8 @@ def test_mask_values_scale_the_products(pkg, oracle, ctx, dev, N):
 
 @pytest.mark.parametrize("M,K,N,density", [(64, 576, 3136, 0.1), (64, 64, 3136, 0.1), (128, 512, 784, 0.1),
                                            (512, 128, 784, 0.1), (256, 256, 64, 0.5), (2, 300, 128, 0.9),
-                                           (64, 576, 32, 0.1), (2, 300, 16, 0.9), (128, 512, 32, 0.3), (16, 4096, 24, 0.5)])
+                                           (64, 576, 32, 0.1), (2, 300, 16, 0.9), (128, 512, 32, 0.3), (16, 4096, 24, 0.5),
+                                           (64, 576, 49, 0.1), (2, 300, 13, 0.9), (128, 512, 201, 0.2), (300, 700, 255, 0.3)])
 def test_tiny_patterns_share_rows_and_passes(pkg, oracle, ctx, dev, M, K, N, density):
     """Layer-sized patterns (tens to hundreds of rows): warps share a row's passes and, where the
     device would still be mostly idle, the nonzeros inside a pass."""
