@@ -24,7 +24,7 @@ HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "dlspm.h")
 OK = 0
 (ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_IO, ERR_FORMAT, ERR_CSR, ERR_NOMEM, ERR_UNSUPPORTED, ERR_NO_DEVICE,
  ERR_TIMEOUT) = range(1, 10)
-OPT_STRICT_FP32, OPT_SPMM_KERNEL, OPT_TILE_MIN_DENSITY = 0, 1, 2
+OPT_STRICT_FP32, OPT_SPMM_KERNEL, OPT_TILE_MIN_DENSITY, OPT_CHECK_INPUT = 0, 1, 2, 3
 SPMM_KERNEL_AUTO, SPMM_KERNEL_GATHER, SPMM_KERNEL_TILED, SPMM_KERNEL_TILED_DENSE = 0, 1, 2, 3
 ATTN_SOFTMAX = 1
 KIND_UNIFORM_PM1, KIND_UNIFORM_01, KIND_NORMAL = 0, 1, 2

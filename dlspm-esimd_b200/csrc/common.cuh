@@ -21,6 +21,7 @@ struct dlspm_ctx {
     int spmm_kernel;  // DLSPM_OPT_SPMM_KERNEL
     int tile_min_density_permille;  // DLSPM_OPT_TILE_MIN_DENSITY
     int tile_min_density_set;       // the caller has set it (a forced kernel choice honours only an explicit threshold)
+    int check_input;                // DLSPM_OPT_CHECK_INPUT
     // Device scratch owned by the context, grown on demand (grouped-launch tables, staging for
     // the host-buffer entry points).  Freed in dlspm_destroy.
     void *scratch;
@@ -67,6 +68,13 @@ static inline int dlspm_use(dlspm_ctx *ctx)
     if (err != cudaSuccess) return dlspm_cuda_fail(ctx, err, "cudaSetDevice");
     return DLSPM_OK;
 }
+
+// DLSPM_OPT_CHECK_INPUT: validates a CSR pattern in device (host) memory when the option is set;
+// DLSPM_ERR_CSR with the reason in ctx->last_error, DLSPM_OK when the option is off (context.cu).
+int dlspm_check_input(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets, const int *column_indices,
+                      cudaStream_t st);
+int dlspm_check_input_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                           const int *column_indices);
 
 // Grows ctx->scratch to at least `bytes` (contents are not preserved).
 int dlspm_scratch_reserve(dlspm_ctx *ctx, size_t bytes);

@@ -122,6 +122,7 @@ extern "C" int dlspm_set_option(dlspm_ctx *ctx, int option, int value)
         if (value < 0 || value > 3) return DLSPM_ERR_INVALID_ARGUMENT;
         ctx->spmm_kernel = value;
         return DLSPM_OK;
+    case DLSPM_OPT_CHECK_INPUT: ctx->check_input = value ? 1 : 0; return DLSPM_OK;
     case DLSPM_OPT_TILE_MIN_DENSITY:
         if (value == -1) {  // back to the default, as if never set
             ctx->tile_min_density_permille = kDefaultTileMinDensity;
@@ -143,6 +144,7 @@ extern "C" int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value)
     case DLSPM_OPT_STRICT_FP32: *value = ctx->strict_fp32; return DLSPM_OK;
     case DLSPM_OPT_SPMM_KERNEL: *value = ctx->spmm_kernel; return DLSPM_OK;
     case DLSPM_OPT_TILE_MIN_DENSITY: *value = ctx->tile_min_density_permille; return DLSPM_OK;
+    case DLSPM_OPT_CHECK_INPUT: *value = ctx->check_input; return DLSPM_OK;
     default: return DLSPM_ERR_INVALID_ARGUMENT;
     }
 }
@@ -451,4 +453,24 @@ extern "C" int dlspm_sanity_check_csr(dlspm_ctx *ctx, int M, int K, int nnz, con
         }
     }
     return DLSPM_ERR_CSR;
+}
+
+int dlspm_check_input(dlspm_ctx *ctx, int M, int K, int nnz, const int *row_offsets, const int *column_indices,
+                      cudaStream_t st)
+{
+    if (!ctx->check_input || M <= 0 || !row_offsets) return DLSPM_OK;
+    char why[160];
+    const int rc = dlspm_sanity_check_csr(ctx, M, K, nnz, row_offsets, column_indices, why, sizeof(why), (void *)st);
+    if (rc == DLSPM_ERR_CSR) snprintf(ctx->last_error, sizeof(ctx->last_error), "input check: %s", why);
+    return rc;
+}
+
+int dlspm_check_input_host(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_offsets,
+                           const int *column_indices)
+{
+    if (!ctx->check_input || M <= 0 || !row_offsets) return DLSPM_OK;
+    char why[160];
+    const int rc = dlspm_sanity_check_csr_host(M, K, N, nnz, row_offsets, column_indices, why, sizeof(why));
+    if (rc != DLSPM_OK) snprintf(ctx->last_error, sizeof(ctx->last_error), "input check: %s", why);
+    return rc;
 }

@@ -318,6 +318,8 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     if (nnz > 0 && N > 0 && (!B || !D)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
+    rc = dlspm_check_input(ctx, M, K, nnz, row_offsets, column_indices, (cudaStream_t)stream);
+    if (rc) return rc;
     if (M == 0 || N == 0) return DLSPM_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int vec = dlspm_vec_width(N, C, B, D, E);

@@ -277,6 +277,8 @@ static int dlspm_spmm_batched_f32_host_impl(dlspm_ctx *ctx, int count, const dls
             (q.nnz > 0 && (!q.values || !q.column_indices)) || ((size_t)q.K * q.N > 0 && !q.B) ||
             ((size_t)q.M * q.N > 0 && !q.C))
             return DLSPM_ERR_INVALID_ARGUMENT;
+        rc = dlspm_check_input_host(ctx, q.M, q.K, q.N, q.nnz, q.row_offsets, q.column_indices);  // DLSPM_OPT_CHECK_INPUT
+        if (rc) return rc;
         largest = std::max(largest, need(q));
     }
     if (count == 0) return DLSPM_OK;
@@ -466,8 +468,12 @@ int rows_batched_host(dlspm_ctx *ctx, int count, const typename T::Problem *prob
     if (!ctx || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     int rc = dlspm_use(ctx);
     if (rc) return rc;
-    for (int i = 0; i < count; i++)
+    for (int i = 0; i < count; i++) {
         if (!T::valid(problems[i])) return DLSPM_ERR_INVALID_ARGUMENT;
+        rc = dlspm_check_input_host(ctx, problems[i].M, problems[i].K, problems[i].N, problems[i].nnz,
+                                    problems[i].row_offsets, problems[i].column_indices);  // DLSPM_OPT_CHECK_INPUT
+        if (rc) return rc;
+    }
     if (count == 0) return DLSPM_OK;
     const size_t budget = (size_t)256 << 20;
     std::vector<int> piece_end;

@@ -319,6 +319,8 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
     int rc = dlspm_use(ctx);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    rc = dlspm_check_input(ctx, M, K, nnz, row_offsets, column_indices, st);
+    if (rc) return rc;
     if (M == 0 || nnz == 0) return DLSPM_OK;
     if (N == 0) {  // empty dot products
         DLSPM_CUDA_TRY(ctx, cudaMemsetAsync(out_values, 0, sizeof(float) * (size_t)nnz, st));

@@ -493,6 +493,12 @@ extern "C" int dlspm_sddmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_sd
     if (count == 0) return DLSPM_OK;
     rc = reject_capture(ctx, (cudaStream_t)stream, "dlspm_sddmm_batched_f32");
     if (rc) return rc;
+    for (int i = 0; i < count && ctx->check_input; i++) {  // DLSPM_OPT_CHECK_INPUT
+        const dlspm_sddmm_problem &q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.nnz < 0 || (q.nnz > 0 && !q.column_indices)) return DLSPM_ERR_INVALID_ARGUMENT;
+        rc = dlspm_check_input(ctx, q.M, q.K, q.nnz, q.row_offsets, q.column_indices, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
     rc = dlspm_scratch_reserve(ctx, dlspm_rows_batched_table_bytes(count));
     if (rc) return rc;
     return dlspm_sddmm_batched_at(ctx, count, problems, ctx->scratch, nullptr, (cudaStream_t)stream);
@@ -506,6 +512,12 @@ extern "C" int dlspm_fused_batched_f32(dlspm_ctx *ctx, int count, const dlspm_fu
     if (count == 0) return DLSPM_OK;
     rc = reject_capture(ctx, (cudaStream_t)stream, "dlspm_fused_batched_f32");
     if (rc) return rc;
+    for (int i = 0; i < count && ctx->check_input; i++) {  // DLSPM_OPT_CHECK_INPUT
+        const dlspm_fused_problem &q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.nnz < 0 || (q.nnz > 0 && !q.column_indices)) return DLSPM_ERR_INVALID_ARGUMENT;
+        rc = dlspm_check_input(ctx, q.M, q.K, q.nnz, q.row_offsets, q.column_indices, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
     rc = dlspm_scratch_reserve(ctx, dlspm_rows_batched_table_bytes(count));
     if (rc) return rc;
     return dlspm_fused_batched_at(ctx, count, problems, ctx->scratch, nullptr, (cudaStream_t)stream);

@@ -346,6 +346,8 @@ extern "C" int dlspm_spmm_csr_f32(dlspm_ctx *ctx, int M, int K, int N, int nnz, 
     if (rc) return rc;
     rc = dlspm_use(ctx);
     if (rc) return rc;
+    rc = dlspm_check_input(ctx, M, K, nnz, row_offsets, column_indices, (cudaStream_t)stream);
+    if (rc) return rc;
     return spmm_launch(ctx, M, N, nnz, values, row_offsets, column_indices, B, C, nullptr, 0,
                        (cudaStream_t)stream);
 }
@@ -359,6 +361,8 @@ extern "C" int dlspm_spmm_csr_f32_planned(dlspm_ctx *ctx, const dlspm_plan *plan
     int rc = check_spmm_args(plan->M, plan->K, N, plan->nnz, values, row_offsets, column_indices, B, C);
     if (rc) return rc;
     rc = dlspm_use(ctx);
+    if (rc) return rc;
+    rc = dlspm_check_input(ctx, plan->M, plan->K, plan->nnz, row_offsets, column_indices, (cudaStream_t)stream);
     if (rc) return rc;
     return spmm_launch(ctx, plan->M, N, plan->nnz, values, row_offsets, column_indices, B, C, plan->row_order,
                        plan->max_row_len, (cudaStream_t)stream);

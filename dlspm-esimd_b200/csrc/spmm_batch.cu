@@ -455,12 +455,26 @@ bool prefer_tiled(const dlspm_ctx *ctx, const dlspm_problem &q, int vec, bool so
 
 }  // namespace
 
+// DLSPM_OPT_CHECK_INPUT for a table of SpMM problems with device pointers.
+static int check_batch_input(dlspm_ctx *ctx, int count, const dlspm_problem *problems, cudaStream_t st)
+{
+    for (int i = 0; i < count && ctx->check_input; i++) {
+        const dlspm_problem &q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.nnz < 0 || (q.nnz > 0 && !q.column_indices)) return DLSPM_ERR_INVALID_ARGUMENT;
+        const int rc = dlspm_check_input(ctx, q.M, q.K, q.nnz, q.row_offsets, q.column_indices, st);
+        if (rc) return rc;
+    }
+    return DLSPM_OK;
+}
+
 extern "C" int dlspm_batch_create(dlspm_ctx *ctx, int count, const dlspm_problem *problems,
                                   dlspm_batch **out)
 {
     if (!ctx || !out || count < 0 || (count > 0 && !problems)) return DLSPM_ERR_INVALID_ARGUMENT;
     *out = nullptr;
     int rc = dlspm_use(ctx);
+    if (rc) return rc;
+    rc = check_batch_input(ctx, count, problems, nullptr);
     if (rc) return rc;
     std::vector<BatchProblem> tab;
     std::vector<long long> starts;
@@ -667,6 +681,8 @@ extern "C" int dlspm_spmm_batched_f32(dlspm_ctx *ctx, int count, const dlspm_pro
     if (rc) return rc;
     if (count == 0) return DLSPM_OK;
     rc = reject_capturing_stream(ctx, (cudaStream_t)stream, "dlspm_spmm_batched_f32");
+    if (rc) return rc;
+    rc = check_batch_input(ctx, count, problems, (cudaStream_t)stream);
     if (rc) return rc;
     rc = dlspm_scratch_reserve(ctx, dlspm_batched_table_bytes(count));
     if (rc) return rc;

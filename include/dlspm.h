@@ -82,7 +82,18 @@ typedef enum dlspm_option {
      * whose fraction of nonzeros is at least value/1000.  Default 450: on B200 the tiled kernel
      * reaches 22.5 TFLOP/s on half-full problems against 15.8 for the row-gather kernel, and loses
      * at 30 % nonzeros (13.9 against 17).  1001 = never; -1 = back to the default, as if never set. */
-    DLSPM_OPT_TILE_MIN_DENSITY = 2
+    DLSPM_OPT_TILE_MIN_DENSITY = 2,
+    /* 1: every entry point that takes a CSR pattern validates it before it launches anything
+     * (row offsets start at 0, end at nnz, never decrease, no row longer than K, every column index
+     * in [0, K)) and returns DLSPM_ERR_CSR with the reason in dlspm_last_error otherwise: device
+     * arrays through the kernel of dlspm_sanity_check_csr, host arrays (the *_host entry points)
+     * through dlspm_sanity_check_csr_host.  The kernels trust their input as the reference's do
+     * (a column index beyond K reads outside B), so this is the mode to run untrusted or freshly
+     * assembled patterns under; it stands in for a memory checker.  A debugging mode: every check
+     * of a device pattern allocates a status word and synchronises the stream, grouped calls check
+     * their problems one by one.  dlspm_spmm_batched_f32_static, which must not allocate, ignores
+     * it.  0 (default): no checks. */
+    DLSPM_OPT_CHECK_INPUT = 3
 } dlspm_option;
 int dlspm_set_option(dlspm_ctx *ctx, int option, int value);
 int dlspm_get_option(const dlspm_ctx *ctx, int option, int *value);

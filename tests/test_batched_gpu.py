@@ -482,3 +482,63 @@ def test_device_side_csr_check(pkg, ctx, dev):
     st, why = ctx.sanity_check_csr(M, K, nnz, to_dev(bad, dev), to_dev(ci, dev))
     assert st == pkg.ERR_CSR and "a_row_offsets[0] != 0" in why
     assert ctx.sanity_check_csr(2, 2, 5, to_dev(np.array([0, 2, 5], np.int32), dev), to_dev(np.zeros(5, np.int32), dev))[1] == "nnz is larger than matrix."
+
+
+def test_check_input_option_rejects_bad_patterns_before_any_launch(pkg, oracle, ctx, dev):
+    """DLSPM_OPT_CHECK_INPUT: with the option on, every entry point that takes a CSR pattern validates
+    it first and returns DLSPM_ERR_CSR (reason in the error text) instead of launching a kernel that
+    would read outside B; outputs stay untouched.  A valid pattern runs as usual.  Off by default."""
+    import torch
+
+    assert ctx.get_option(pkg.OPT_CHECK_INPUT) == 0
+    M, K, N = 200, 150, 64
+    ro, ci = csr_bernoulli(pkg, M, K, 0.1, 78)
+    nnz = int(ci.size)
+    bad = ci.copy()
+    bad[nnz // 3] = K + 5  # would read beyond the last row of B
+    vals = pkg.gen_dense_host(nnz, 78, 2)
+    B = dense(pkg, K, N, 78, 10)
+    A = dense(pkg, M, N, 78, 11)
+    d_ro, d_ci, d_bad, d_v, d_B, d_A = (to_dev(x, dev) for x in (ro, ci, bad, vals, B, A))
+    C = torch.full((M * N,), float("nan"), device=dev)
+    out = torch.full((nnz,), float("nan"), device=dev)
+    ctx.set_option(pkg.OPT_CHECK_INPUT, 1)
+    try:
+        calls = {
+            "spmm": lambda c: ctx.spmm(M, K, N, nnz, d_v, d_ro, c, d_B, C),
+            "sddmm": lambda c: ctx.sddmm(M, K, N, nnz, d_ro, c, d_A, d_B, out),
+            "fused": lambda c: ctx.fused(M, K, N, nnz, d_ro, c, d_A, d_B, d_B, C),
+        }
+        for name, call in calls.items():
+            with pytest.raises(pkg.DlspmError) as e:
+                call(d_bad)
+            assert e.value.status == pkg.ERR_CSR, name
+            assert "a_column_indices[i] >= KSZ" in str(e.value) and f"i = {nnz // 3}" in str(e.value), name
+        arr = pkg.ProblemArray(2)
+        arr.set(0, M, K, N, nnz, d_v, d_ro, d_ci, d_B, C)
+        arr.set(1, M, K, N, nnz, d_v, d_ro, d_bad, d_B, torch.empty(M * N, device=dev))
+        for call in (lambda: ctx.spmm_batched(arr), lambda: ctx.batch_create(arr)):
+            with pytest.raises(pkg.DlspmError) as e:
+                call()
+            assert e.value.status == pkg.ERR_CSR
+        rows = pkg.RowProblemArray("sddmm", 1)
+        rows.set_sddmm(0, M, K, N, nnz, d_ro, d_bad, d_A, d_B, out)
+        with pytest.raises(pkg.DlspmError) as e:
+            ctx.sddmm_batched(rows)
+        assert e.value.status == pkg.ERR_CSR
+        host = pkg.ProblemArray(1)
+        Ch = np.full(M * N, np.nan, dtype=np.float32)
+        host.set(0, M, K, N, nnz, vals, ro, bad, np.ascontiguousarray(B).ravel(), Ch, host=True)
+        with pytest.raises(pkg.DlspmError) as e:
+            ctx.spmm_batched_host(host)
+        assert e.value.status == pkg.ERR_CSR
+        torch.cuda.synchronize()
+        assert torch.isnan(C).all() and torch.isnan(out).all() and np.isnan(Ch).all(), "a rejected call wrote output"
+        # the valid pattern passes the check and gives the usual result
+        calls["spmm"](d_ci)
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option(pkg.OPT_CHECK_INPUT, 0)
+    bad_count, worst = oracle.violations(oracle.spmm(vals, ro, ci, B, M, N), C.cpu().numpy().reshape(M, N),
+                                         oracle.spmm_scale(vals, ro, ci, B, M, N), TOL)
+    assert bad_count == 0, worst
