@@ -6,6 +6,8 @@
 // no atomics (the reference's v4 kernel adds partial sums atomically and needs a zeroed output,
 // SDDMM/sddmm-esimd-fromfile_v4.hpp:161), so results are deterministic and every output element is
 // written exactly once.
+#include <cstdint>
+
 #include "common.cuh"
 #include "sddmm_device.cuh"
 
@@ -22,7 +24,7 @@ constexpr int kWarps = 8;
 // picks by the number of warps.  The one-chunk layout needs 32 registers anyway.  The 32-lane layouts
 // are held to five (four chunks per lane) and four (eight chunks) resident blocks: 8192 x 2048 with
 // N = 512 went 296 -> 255 us, with N = 1024 754 -> 480 us; one block more lost 15 to 35 % again.
-template <int G, int R, bool KSPLIT, bool CAP = false>
+template <int G, int R, bool KSPLIT, bool CAP = false, bool WIDE = false>
 __global__ void __launch_bounds__(kWarps * 32, CAP ? 8 : ((G == 32 && R == 4 && !KSPLIT) ? 5 : ((G == 32 && R == 8 && !KSPLIT) ? 4 : 0)))
 sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ lhs, const float *__restrict__ rhs, float *__restrict__ out,
@@ -44,7 +46,8 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     const int end = __ldg(row_offsets + row + 1);
     if (start >= end) return;
     float4 a[R];
-    load_row_chunks<G, R>(lhs4, chunks, t, a);
+    if constexpr (WIDE) load_row_pair(lhs4, t, a);  // N = 32, 32-byte aligned operands: see sddmm_pass_dealt_wide
+    else load_row_chunks<G, R>(lhs4, chunks, t, a);
     // the column indices of the next pass are fetched before this pass is computed, so that their
     // latency does not sit in front of the rhs gathers of every pass
     int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
@@ -57,7 +60,9 @@ sddmm_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
             if (p < end && (t & kmask) == ksub) out[p] = mask ? __ldg(mask + p) * r : r;
         } else {
             // nonzeros dealt to the lane groups in turn: this lane ends up with nonzero `q` of the row
-            const float r = sddmm_pass_dealt<G, R>(a, rhs4, chunks, col, g, t);
+            float r;
+            if constexpr (WIDE) r = sddmm_pass_dealt_wide(a, rhs4, col, g, t);
+            else r = sddmm_pass_dealt<G, R>(a, rhs4, chunks, col, g, t);
             const int q = base + sddmm_dealt_slot(G, g, t);
             if (q < end) out[q] = mask ? __ldg(mask + q) * r : r;
         }
@@ -243,7 +248,7 @@ inline int sddmm_wave_shift(long long blocks, long long resident, double avg_row
 template <int G, int R>
 void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rhs, float *out, int M,
                  int chunks, const float *mask, int split_shift, int k_shift, int sm_count, cudaStream_t st,
-                 double avg_row = 0.0)
+                 double avg_row = 0.0, bool wide = false)
 {
     if (split_shift == 0 && k_shift == 0 && avg_row > 0.0) {
         static int per_sm = 0;  // resident blocks of the plain build of this layout
@@ -264,6 +269,12 @@ void launch_fast(const int *ro, const int *ci, const float *lhs, const float *rh
         const long long w6 = (blocks + 6LL * sm_count - 1) / (6LL * sm_count), w8 = (blocks + 8LL * sm_count - 1) / (8LL * sm_count);
         if (k_shift == 0 && (double)w8 * 8.0 * 1.07 < (double)w6 * 6.0) {
             sddmm_rows_kernel<G, R, false, true><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask, split_shift, 0);
+            return;
+        }
+    }
+    if constexpr (G == 4 && R == 2) {
+        if (wide && k_shift == 0) {
+            sddmm_rows_kernel<G, R, false, false, true><<<blocks, kWarps * 32, 0, st>>>(ro, ci, lhs, rhs, out, M, chunks, mask, split_shift, 0);
             return;
         }
     }
@@ -340,7 +351,16 @@ int sddmm_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         // by the index within a group, so at most 4 warps can do that with groups of 4.
         if (chunks <= 8 && kshift <= 2) {
             if (chunks <= 4) launch_fast<4, 1>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, avg_row);
-            else launch_fast<4, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, avg_row);
+            else {
+                // N = 32 with 32-byte aligned operands: one 256-bit load per lane and nonzero.  That build
+                // needs 42 registers instead of 32 (five resident blocks instead of eight), which costs a
+                // launch of less than about a wave more than the halved L1 traffic gains (GFLOP/s at 30 %
+                // nonzeros: 1024 x 1024 1977 -> 1557, 4096 x 4096 6336 -> 5898, but 8192 x 8192
+                // 6498 -> 7182, 16384 x 4096 6862 -> 9398, 32768 x 8192 7133 -> 8979): from 8192 rows on.
+                const bool wide = chunks == 8 && ((uintptr_t)lhs % 32) == 0 && ((uintptr_t)rhs % 32) == 0 &&
+                                  (long long)blocks * 10 >= 69LL * ctx->sm_count;
+                launch_fast<4, 2>(row_offsets, column_indices, lhs, rhs, out_values, M, chunks, mask, shift, kshift, ctx->sm_count, st, avg_row, wide);
+            }
             DLSPM_CUDA_TRY(ctx, cudaGetLastError());
             return DLSPM_OK;
         }

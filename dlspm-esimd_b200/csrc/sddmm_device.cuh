@@ -50,6 +50,48 @@ __device__ __forceinline__ void load_row_chunks(const float4 *__restrict__ row4,
     }
 }
 
+// 32 bytes in one load (sm_100 has 256-bit global loads).  `p` must be 32-byte aligned.
+__device__ __forceinline__ void ldg256(const float4 *__restrict__ p, float4 &lo, float4 &hi)
+{
+    asm("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w), "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w)
+                 : "l"(p));
+}
+
+// Rows of exactly 32 floats (eight chunks) whose operands are 32-byte aligned, groups of four lanes:
+// lane t owns the chunks 2t and 2t+1, i.e. 32 consecutive bytes, and fetches them with ONE 256-bit
+// load, so a group reads a whole 128-byte row per load instruction.  With 16-byte loads (chunks t and
+// 4+t) a warp-wide load touches eight rows but uses only half of each 128-byte line, twice the L1
+// wavefronts per nonzero: the N = 32 launches sat at 88 % of the L1 data pipe.  Same dealing of the
+// nonzeros and same result placement as sddmm_pass_dealt<4, 2>; the lanes' partial sums cover other
+// elements, so the bits can differ from the 16-byte form in the last place.
+__device__ __forceinline__ void load_row_pair(const float4 *__restrict__ row4, int t, float4 (&a)[2])
+{
+    a[0] = __ldg(row4 + 2 * t);
+    a[1] = __ldg(row4 + 2 * t + 1);
+}
+
+__device__ __forceinline__ float sddmm_pass_dealt_wide(const float4 (&a)[2], const float4 *__restrict__ rhs4,
+                                                       int col, int g, int t)
+{
+    constexpr int G = 4, NG = 8, kChunks = 8;
+    float part[G];
+#pragma unroll
+    for (int k = 0; k < G; k++) {
+        const int c = __shfl_sync(0xffffffffu, col, k * NG + g);
+        float acc = 0.f;
+        if (c >= 0) {
+            float4 lo, hi;
+            ldg256(rhs4 + (size_t)c * kChunks + 2 * t, lo, hi);
+            acc = dot4(a[0], lo, acc);
+            acc = dot4(a[1], hi, acc);
+        }
+        part[k] = acc;
+    }
+    group_transpose_reduce<G>(part, t);
+    return part[0];
+}
+
 // One pass of sampled dot products: col = this lane's column index of nonzero base+lane (or -1
 // past the end of the row).  On return part0 on lane g*G+t is dot(lhs_row, rhs[col of that lane]).
 // Adds to part[k] the partial dot product of this lane for the k-th nonzero of its group.  `chunks`
