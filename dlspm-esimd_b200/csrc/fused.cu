@@ -14,6 +14,8 @@
 // (sparse attention).  The softmax is the streaming form: a running maximum and a running sum per
 // row, and the partial output row is rescaled whenever the maximum grows, so a row is still read
 // once and nothing is written besides the output row.
+#include <cstdint>
+
 #include "common.cuh"
 #include "fused_device.cuh"
 #include "sddmm_device.cuh"
@@ -32,7 +34,7 @@ constexpr int kWarps = 8;
 //  - 32 lanes x four chunks (d = 260..512): 64 registers for four resident blocks instead of two:
 //    1.3 to 1.5x faster once the pattern has more rows than the uncapped build keeps resident
 //    (8192 x 2048, d = 512: 637 -> 479 us), 12 % slower below that.
-template <int G, int R, int MODE, bool CAP = false>
+template <int G, int R, int MODE, bool CAP = false, bool WIDE = false>
 __global__ void __launch_bounds__(kWarps * 32, CAP ? (G == 8 ? 8 : 4) : 0)
 fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
                   const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
@@ -44,14 +46,15 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
     const int g = lane / G, t = lane % G;
     const float4 *c4 = reinterpret_cast<const float4 *>(c) + (size_t)row * (size_t)chunks;
     float4 q[R];
-    load_row_chunks<G, R>(c4, chunks, t, q);
+    if constexpr (WIDE) load_row_pair(c4, t, q);  // rows of 32 floats, 32-byte aligned: lane t owns chunks 2t, 2t + 1
+    else load_row_chunks<G, R>(c4, chunks, t, q);
     float4 acc[R];
 #pragma unroll
     for (int r = 0; r < R; r++) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
     float run_max = -INFINITY, run_sum = 0.f;
-    fused_row_passes<G, R, MODE>(cols, q, reinterpret_cast<const float4 *>(b), reinterpret_cast<const float4 *>(d),
-                                 chunks, __ldg(row_offsets + row), __ldg(row_offsets + row + 1), 32, scale, lane,
-                                 acc, run_max, run_sum);
+    fused_row_passes<G, R, MODE, WIDE>(cols, q, reinterpret_cast<const float4 *>(b), reinterpret_cast<const float4 *>(d),
+                                       chunks, __ldg(row_offsets + row), __ldg(row_offsets + row + 1), 32, scale, lane,
+                                       acc, run_max, run_sum);
     if constexpr (MODE == kSoftmax) {
         const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;  // empty row: zeros
 #pragma unroll
@@ -66,7 +69,7 @@ fused_rows_kernel(const int *__restrict__ row_offsets, const int *__restrict__ c
         float4 *e4 = reinterpret_cast<float4 *>(e) + (size_t)row * (size_t)chunks;
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int idx = r * G + t;
+            const int idx = WIDE ? 2 * t + r : r * G + t;
             if (idx < chunks) e4[idx] = acc[r];
         }
     }
@@ -251,7 +254,8 @@ inline int fused_wave_shift(long long blocks, long long resident, double avg_row
 
 template <int G, int R, int MODE>
 void launch_fast(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e,
-                 int M, int chunks, float scale, int split_shift, int sm_count, cudaStream_t st, double avg_row = 0.0)
+                 int M, int chunks, float scale, int split_shift, int sm_count, cudaStream_t st, double avg_row = 0.0,
+                 bool wide = false)
 {
     if (split_shift == 0 && avg_row > 0.0) {
         static int per_sm = 0;  // resident blocks of the plain build of this layout
@@ -285,6 +289,12 @@ void launch_fast(const int *ro, const int *ci, const float *c, const float *b, c
         const long long w6 = (blocks + 6LL * sm_count - 1) / (6LL * sm_count), w8 = (blocks + 8LL * sm_count - 1) / (8LL * sm_count);
         if ((double)w8 * 8.0 * 1.07 < (double)w6 * 6.0) {
             fused_rows_kernel<G, R, MODE, true><<<(unsigned)blocks, kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
+            return;
+        }
+    }
+    if constexpr (G == 4 && R == 2) {
+        if (wide) {  // rows of 32 floats, 32-byte aligned operands, a long launch: 256-bit loads
+            fused_rows_kernel<G, R, MODE, false, true><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, chunks, scale);
             return;
         }
     }
@@ -330,7 +340,11 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         if (chunks <= 8) {  // rows of up to 32 floats: groups of four lanes, as in the SDDMM kernel (16384 x 4096 at
                             // 30 %, d = 16: 389 -> 184 us; 8192 x 8192 at 30 %, d = 32: 462 -> 357 us)
             if (chunks <= 4) launch_fast<4, 1, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
-            else launch_fast<4, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+            else {
+                const bool wide = chunks == 8 && ((uintptr_t)C % 32) == 0 && ((uintptr_t)B % 32) == 0 && ((uintptr_t)D % 32) == 0 &&
+                                  (long long)M * 10 >= 69LL * kWarps * ctx->sm_count;
+                launch_fast<4, 2, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M, wide);
+            }
             DLSPM_CUDA_TRY(ctx, cudaGetLastError());
             return DLSPM_OK;
         }

@@ -28,7 +28,7 @@ __device__ __forceinline__ float warp_sum(float v)
 // The passes base, base + stride, ... of one row: scores as in the SDDMM kernel, then the update of
 // the lane's partial output row.  On return acc holds this lane group's partial sums (relative to
 // run_max in softmax mode).
-template <int G, int R, int MODE>
+template <int G, int R, int MODE, bool WIDE = false>
 __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, const float4 (&q)[R],
                                                  const float4 *__restrict__ b4, const float4 *__restrict__ d4,
                                                  int chunks, int start, int end, int stride, float scale, int lane,
@@ -43,7 +43,9 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
         col_next = p + stride < end ? __ldg(cols + p + stride) : -1;
         // nonzeros dealt to the lane groups in turn (see sddmm_pass_dealt): this lane's score belongs
         // to nonzero base + sddmm_dealt_slot of the row, whose column sits on lane sddmm_dealt_slot
-        float score = sddmm_pass_dealt<G, R>(q, b4, chunks, col, g, t);
+        float score;
+        if constexpr (WIDE) score = sddmm_pass_dealt_wide(q, b4, col, g, t);  // G = 4, R = 2, rows of 32 floats
+        else score = sddmm_pass_dealt<G, R>(q, b4, chunks, col, g, t);
         if constexpr (MODE == kScaled) score *= scale;
         if constexpr (MODE == kSoftmax) {
             // streaming softmax: weights relative to the running maximum; the partial row and the
@@ -67,7 +69,21 @@ __device__ __forceinline__ void fused_row_passes(const int *__restrict__ cols, c
         for (int k = 0; k < G; k++) {
             const int cc = __shfl_sync(0xffffffffu, col, k * (32 / G) + g);  // the group's k-th nonzero
             const float s = __shfl_sync(0xffffffffu, score, g * G + k);
-            if (cc >= 0) {
+            if constexpr (WIDE) {
+                // lane t owns the chunks 2t and 2t + 1 of the row: one 256-bit load (see sddmm_pass_dealt_wide)
+                if (cc >= 0) {
+                    float4 lo, hi;
+                    ldg256(d4 + (size_t)cc * 8 + 2 * t, lo, hi);
+                    acc[0].x = fmaf(s, lo.x, acc[0].x);
+                    acc[0].y = fmaf(s, lo.y, acc[0].y);
+                    acc[0].z = fmaf(s, lo.z, acc[0].z);
+                    acc[0].w = fmaf(s, lo.w, acc[0].w);
+                    acc[R - 1].x = fmaf(s, hi.x, acc[R - 1].x);
+                    acc[R - 1].y = fmaf(s, hi.y, acc[R - 1].y);
+                    acc[R - 1].z = fmaf(s, hi.z, acc[R - 1].z);
+                    acc[R - 1].w = fmaf(s, hi.w, acc[R - 1].w);
+                }
+            } else if (cc >= 0) {
                 const float4 *drow = d4 + (size_t)cc * (size_t)chunks;
 #pragma unroll
                 for (int r = 0; r < R; r++) {
