@@ -105,3 +105,28 @@ def test_few_long_rows_are_shared_between_warps(pkg, oracle, ctx, dev, K, densit
     k = dense(pkg, K, N, 43, 12)
     v = dense(pkg, K, N, 43, 13)
     check(oracle, ro, ci, q, k, v, M, N, run_fused(ctx, dev, M, K, N, ro, ci, q, k, v))
+
+
+@pytest.mark.parametrize("offset_floats", [0, 4])
+def test_rows_of_32_floats_in_a_long_launch(pkg, oracle, ctx, dev, offset_floats):
+    """d = 32 with 8192 rows or more: 32-byte aligned operands take the build with 256-bit loads for
+    the gathers of B and D; operands aligned to 16 bytes only must take the 16-byte build."""
+    import torch
+
+    M, K, N = 9000, 600, 32
+    ro, ci = csr_bernoulli(pkg, M, K, 0.06, seed=92)
+    q = dense(pkg, M, N, 92, 11, kind=pkg.KIND_NORMAL)
+    k = dense(pkg, K, N, 92, 12, kind=pkg.KIND_NORMAL)
+    v = dense(pkg, K, N, 92, 13, kind=pkg.KIND_NORMAL)
+
+    def place(a):
+        t = torch.empty(a.size + 8, device=dev)[offset_floats:offset_floats + a.size]
+        t.copy_(torch.from_numpy(np.ascontiguousarray(a).ravel()))
+        return t
+
+    d_q, d_k, d_v = place(q), place(k), place(v)
+    assert d_k.data_ptr() % 32 == (16 if offset_floats else 0)
+    out = torch.full((M * N,), float("nan"), device=dev)
+    ctx.fused(M, K, N, int(ci.size), to_dev(ro, dev), to_dev(ci, dev), d_q, d_k, d_v, out)
+    torch.cuda.synchronize()
+    check(oracle, ro, ci, q, k, v, M, N, out.cpu().numpy().reshape(M, N))

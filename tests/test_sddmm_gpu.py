@@ -204,3 +204,26 @@ def test_tiny_patterns_share_rows_and_passes(pkg, oracle, ctx, dev, M, K, N, den
     rhs = dense(pkg, K, N, 1000 + M, 12, kind=pkg.KIND_NORMAL)
     check(oracle, ro, ci, lhs, rhs, M, N, run_sddmm(ctx, dev, M, K, N, ro, ci, lhs, rhs))
 
+
+
+@pytest.mark.parametrize("offset_floats", [0, 4])
+def test_rows_of_32_floats_in_a_long_launch(pkg, oracle, ctx, dev, offset_floats):
+    """N = 32 with 8192 rows or more: 32-byte aligned operands take the build with one 256-bit load per
+    lane and nonzero; operands aligned to 16 bytes only (offset of four floats) must take the 16-byte
+    build.  Both against the oracle, with empty rows and a ragged last pass in most rows."""
+    import torch
+
+    M, K, N = 9000, 700, 32
+    ro, ci = csr_bernoulli(pkg, M, K, 0.07, seed=91)
+    nnz = int(ci.size)
+    lhs = dense(pkg, M, N, 91, 11, kind=pkg.KIND_NORMAL)
+    rhs = dense(pkg, K, N, 91, 12, kind=pkg.KIND_NORMAL)
+    d_lhs = torch.empty(M * N + 8, device=dev)[offset_floats:offset_floats + M * N]
+    d_rhs = torch.empty(K * N + 8, device=dev)[offset_floats:offset_floats + K * N]
+    d_lhs.copy_(torch.from_numpy(np.ascontiguousarray(lhs).ravel()))
+    d_rhs.copy_(torch.from_numpy(np.ascontiguousarray(rhs).ravel()))
+    assert d_rhs.data_ptr() % 32 == (16 if offset_floats else 0)
+    out = torch.full((nnz,), float("nan"), device=dev)
+    ctx.sddmm(M, K, N, nnz, to_dev(ro, dev), to_dev(ci, dev), d_lhs, d_rhs, out)
+    torch.cuda.synchronize()
+    check(oracle, ro, ci, lhs, rhs, M, N, out.cpu().numpy())
