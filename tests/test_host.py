@@ -28,6 +28,20 @@ def test_library_exports_every_declared_symbol(pkg):
     assert sorted(pkg.exported_names()) == names
 
 
+def test_python_constants_match_the_header(pkg):
+    """Option numbers and status codes of the ctypes binding are the header's."""
+    text = open(pkg.HEADER_PATH).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    enums = {name: int(value) for name, value in re.findall(r"\b(DLSPM_[A-Z0-9_]+)\s*=\s*(-?\d+)", text)}
+    options = {k: v for k, v in enums.items() if k.startswith("DLSPM_OPT_")}
+    assert len(options) == 4
+    for name, value in options.items():
+        assert getattr(pkg, name[len("DLSPM_"):]) == value, name
+    for name, value in enums.items():
+        if name.startswith("DLSPM_ERR_") or name == "DLSPM_OK":
+            assert getattr(pkg, name[len("DLSPM_"):]) == value, name
+
+
 def test_strerror_and_no_device_failure(pkg):
     assert pkg.strerror(pkg.OK) == "ok"
     assert pkg.strerror(pkg.ERR_IO) == "Error opening file!"  # the reference's exception text
