@@ -232,6 +232,108 @@ fused_generic_kernel(const int *__restrict__ row_offsets, const int *__restrict_
     }
 }
 
+// Widths that rule out 128-bit loads (N not a multiple of 4, or unaligned operands) up to 256 floats:
+// the group layout of the fast path with scalar elements, as in the SDDMM kernel for such widths.
+// Lane t of a group of G lanes owns the elements e*G + t of a dense row; the row of C stays in
+// registers, scores are formed with dealt passes and the transposing butterfly, every lane group
+// gathers the D rows of its own nonzeros, and the groups' partial rows are added with shuffles when
+// the row is done.  The any-width kernel above runs a full-warp reduction per nonzero and re-reads
+// the row of C every time.
+template <int G, int E, int MODE>
+__global__ void __launch_bounds__(kWarps * 32)
+fused_rows_scalar_kernel(const int *__restrict__ row_offsets, const int *__restrict__ cols,
+                         const float *__restrict__ c, const float *__restrict__ b, const float *__restrict__ d,
+                         float *__restrict__ e, int M, int N, float scale)
+{
+    constexpr int NG = 32 / G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarps + warp;
+    if (row >= M) return;
+    const int g = lane / G, t = lane % G;
+    const int start = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
+    const float *crow = c + (size_t)row * (size_t)N;
+    float q[E], acc[E];
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const int idx = i * G + t;
+        q[i] = idx < N ? __ldg(crow + idx) : 0.f;
+        acc[i] = 0.f;
+    }
+    [[maybe_unused]] float run_max = -INFINITY, run_sum = 0.f;
+    int col_next = start + lane < end ? __ldg(cols + start + lane) : -1;
+    for (int base = start; base < end; base += 32) {
+        const int col = col_next;
+        col_next = base + 32 + lane < end ? __ldg(cols + base + 32 + lane) : -1;
+        float part[G];
+#pragma unroll
+        for (int k = 0; k < G; k++) {
+            const int cc = __shfl_sync(0xffffffffu, col, k * NG + g);
+            float dot = 0.f;
+            if (cc >= 0) {
+                const float *brow = b + (size_t)cc * (size_t)N;
+#pragma unroll
+                for (int i = 0; i < E; i++) {
+                    const int idx = i * G + t;
+                    if (idx < N) dot = fmaf(q[i], __ldg(brow + idx), dot);
+                }
+            }
+            part[k] = dot;
+        }
+        group_transpose_reduce<G>(part, t);
+        float score = part[0];  // of nonzero base + sddmm_dealt_slot(G, g, t), whose column sits on that lane
+        if constexpr (MODE == kScaled) score *= scale;
+        if constexpr (MODE == kSoftmax) {
+            const bool stored = base + sddmm_dealt_slot(G, g, t) < end;
+            const float x = stored ? score * scale : -INFINITY;
+            const float m_new = fmaxf(run_max, warp_max(x));
+            const float corr = expf(run_max - m_new);
+            score = stored ? expf(x - m_new) : 0.f;
+            run_sum = run_sum * corr + warp_sum(score);
+            run_max = m_new;
+#pragma unroll
+            for (int i = 0; i < E; i++) acc[i] *= corr;
+        }
+#pragma unroll
+        for (int k = 0; k < G; k++) {
+            const int cc = __shfl_sync(0xffffffffu, col, k * NG + g);  // the group's k-th nonzero
+            const float s = __shfl_sync(0xffffffffu, score, g * G + k);
+            if (cc >= 0) {
+                const float *drow = d + (size_t)cc * (size_t)N;
+#pragma unroll
+                for (int i = 0; i < E; i++) {
+                    const int idx = i * G + t;
+                    if (idx < N) acc[i] = fmaf(s, __ldg(drow + idx), acc[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int s = G; s < 32; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], s);
+    }
+    [[maybe_unused]] const float inv = run_sum > 0.f ? 1.f / run_sum : 0.f;  // empty row: zeros
+    if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const int idx = i * G + t;
+            if constexpr (MODE == kSoftmax) acc[i] *= inv;
+            if (idx < N) e[(size_t)row * (size_t)N + idx] = acc[i];
+        }
+    }
+}
+
+template <int G, int MODE>
+void launch_scalar(const int *ro, const int *ci, const float *c, const float *b, const float *d, float *e, int M, int N,
+                   float scale, cudaStream_t st)
+{
+    const unsigned blocks = (unsigned)dlspm_ceil_div(M, kWarps);
+    const int per_lane = dlspm_ceil_div(N, G);
+    if (per_lane <= 2) fused_rows_scalar_kernel<G, 2, MODE><<<blocks, kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, N, scale);
+    else if (per_lane <= 4) fused_rows_scalar_kernel<G, 4, MODE><<<blocks, kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, N, scale);
+    else fused_rows_scalar_kernel<G, 8, MODE><<<blocks, kWarps * 32, 0, st>>>(ro, ci, c, b, d, e, M, N, scale);
+}
+
 // Patterns of one to a few waves of thread blocks, as in the SDDMM launcher: two or four warps per row
 // make the waves finer where the last one would be nearly empty (6144 or 12288 rows).  A shared row
 // costs more here than in SDDMM (every warp loads the row of C, partial rows are combined through
@@ -354,6 +456,10 @@ int fused_launch(dlspm_ctx *ctx, int M, int K, int N, int nnz, const int *row_of
         else if (G == 16) launch_fast<16, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
         else if (G == 32 && R == 4) launch_fast<32, 4, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
         else launch_fast<32, 8, MODE>(row_offsets, column_indices, C, B, D, E, M, chunks, scale, shift, ctx->sm_count, st, (double)nnz / (double)M);
+    } else if (N <= 256) {  // no 128-bit loads: the group layout with scalar elements
+        if (N <= 64) launch_scalar<8, MODE>(row_offsets, column_indices, C, B, D, E, M, N, scale, st);
+        else if (N <= 128) launch_scalar<16, MODE>(row_offsets, column_indices, C, B, D, E, M, N, scale, st);
+        else launch_scalar<32, MODE>(row_offsets, column_indices, C, B, D, E, M, N, scale, st);
     } else {
         fused_generic_kernel<MODE><<<dlspm_ceil_div(M, kWarps), kWarps * 32, 0, st>>>(row_offsets, column_indices, C, B, D, E, M, N, scale);
     }

@@ -43,7 +43,7 @@ def test_config4_band_mask_4096_d64(pkg, oracle, ctx, dev, softmax):
           run_attention(pkg, ctx, dev, M, K, N, ro, ci, q, k, v, scale, softmax))
 
 
-@pytest.mark.parametrize("N", [1, 3, 4, 8, 16, 32, 36, 64, 100, 128, 130, 256, 384, 1024, 1040])
+@pytest.mark.parametrize("N", [1, 3, 4, 8, 13, 16, 32, 36, 49, 64, 65, 100, 127, 128, 130, 201, 255, 256, 258, 384, 1024, 1040])
 @pytest.mark.parametrize("softmax", [False, True])
 def test_feature_dimensions(pkg, oracle, ctx, dev, N, softmax):
     M, K = 45, 70

@@ -38,7 +38,7 @@ def test_config4_band_mask_4096_d64(pkg, oracle, ctx, dev):
     check(oracle, ro, ci, q, k, v, M, N, run_fused(ctx, dev, M, K, N, ro, ci, q, k, v))
 
 
-@pytest.mark.parametrize("N", [1, 3, 4, 8, 16, 32, 36, 64, 100, 128, 130, 256, 384, 1024, 1040])
+@pytest.mark.parametrize("N", [1, 3, 4, 8, 13, 16, 32, 36, 49, 64, 65, 100, 127, 128, 130, 201, 255, 256, 258, 384, 1024, 1040])
 def test_feature_dimensions(pkg, oracle, ctx, dev, N):
     M, K = 45, 70
     ro, ci = csr_bernoulli(pkg, M, K, 0.3, seed=300 + N)
