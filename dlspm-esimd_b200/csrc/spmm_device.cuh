@@ -143,23 +143,21 @@ __device__ __forceinline__ int2 spmm_first_pairs(const float *__restrict__ value
     return p < end ? make_int2(__ldg(cols + p), __float_as_int(__ldg(values + p))) : make_int2(0, 0);
 }
 
-// stage: 32 int2 slots private to this warp.  PRE: `first` holds spmm_first_pairs of this row.
-template <int VEC, int U, bool STRICT, int J = 0, bool PRE = false>
-__device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
-                                                   const int *__restrict__ cols, int start, int end,
-                                                   const float *__restrict__ B, float *__restrict__ Crow,
-                                                   int N, int n0, int lane, int2 *stage,
-                                                   int2 first = make_int2(0, 0))
+// The sums of one row for one slab: acc[u][v] for the columns cidx[u] + v (computed here), products
+// added in CSR order from 0.0f.  stage: 32 int2 slots private to this warp.  PRE: `first` holds
+// spmm_first_pairs of this row.
+template <int VEC, int U, bool STRICT, int J, bool PRE>
+__device__ __forceinline__ void spmm_warp_row_sums(const float *__restrict__ values, const int *__restrict__ cols,
+                                                   int start, int end, const float *__restrict__ B, int N, int n0,
+                                                   int lane, int2 *stage, int2 first, int (&cidx)[U],
+                                                   float (&acc)[U][VEC])
 {
-    float acc[U][VEC];
-    int cidx[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
         cidx[u] = n0 + (u * 32 + lane) * VEC;
 #pragma unroll
         for (int v = 0; v < VEC; v++) acc[u][v] = 0.0f;
     }
-
     for (int base = start; base < end; base += 32) {
         const int p = base + lane;
         int2 cv = make_int2(0, 0);
@@ -170,6 +168,20 @@ __device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ val
         spmm_accumulate_staged<VEC, U, STRICT, J>(stage, min(32, end - base), B, N, cidx, acc);
         __syncwarp();
     }
+}
+
+// One row of C for one slab, written to Crow.  stage: 32 int2 slots private to this warp.  PRE: `first`
+// holds spmm_first_pairs of this row.
+template <int VEC, int U, bool STRICT, int J = 0, bool PRE = false>
+__device__ __forceinline__ void spmm_warp_row_slab(const float *__restrict__ values,
+                                                   const int *__restrict__ cols, int start, int end,
+                                                   const float *__restrict__ B, float *__restrict__ Crow,
+                                                   int N, int n0, int lane, int2 *stage,
+                                                   int2 first = make_int2(0, 0))
+{
+    float acc[U][VEC];
+    int cidx[U];
+    spmm_warp_row_sums<VEC, U, STRICT, J, PRE>(values, cols, start, end, B, N, n0, lane, stage, first, cidx, acc);
 #pragma unroll
     for (int u = 0; u < U; u++) {
         if (cidx[u] < N) store_vec_streaming<VEC>(Crow + cidx[u], acc[u]);
