@@ -91,7 +91,8 @@ typedef enum dlspm_option {
      * (a column index beyond K reads outside B), so this is the mode to run untrusted or freshly
      * assembled patterns under; it stands in for a memory checker.  A debugging mode: every check
      * of a device pattern allocates a status word and synchronises the stream, grouped calls check
-     * their problems one by one.  dlspm_spmm_batched_f32_static, which must not allocate, ignores
+     * their problems one by one; not for calls on a capturing stream (the check would end the
+     * capture with an error).  dlspm_spmm_batched_f32_static, which must not allocate, ignores
      * it.  0 (default): no checks. */
     DLSPM_OPT_CHECK_INPUT = 3
 } dlspm_option;
