@@ -54,3 +54,19 @@ def test_interchanged_loop_has_the_same_bits(pkg, oracle):
     a = oracle.spmm(vals, ro, ci, B, M, N)
     b = oracle.spmm(vals, ro, ci, B, M, N, threads=3, fast_order=True)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_profile_summaries_keep_the_profiler_rules():
+    """Every ncu command quoted under profiles/ leaves the GPU clocks alone and names one kernel."""
+    import glob
+    import os
+    import re
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "profiles")
+    files = sorted(glob.glob(os.path.join(root, "*.md")))
+    assert files, "no profile summaries"
+    for path in files:
+        for line in open(path):
+            if re.match(r"\s+ncu\s", line):
+                assert "--clock-control none" in line, f"{os.path.basename(path)}: {line.strip()}"
+                assert "--set full" not in line or " -k " in line, f"{os.path.basename(path)}: a full capture of every kernel"
