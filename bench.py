@@ -978,7 +978,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed launch")
     ap.add_argument("--tile-density", type=int, default=None, help="DLSPM_OPT_TILE_MIN_DENSITY in thousandths")
     ap.add_argument("--spmm-kernel", type=int, default=0, help="0 auto, 1 row-gather only, 2 tiled where possible, 3 tiled with zeros")
-    ap.add_argument("--e2e-bytes", type=float, default=16e9, help="host bytes of the e2e sample per rank")
+    ap.add_argument("--e2e-bytes", type=float, default=None,
+                    help="host bytes of the e2e sample per rank (default: 16e9 on one GPU, 4e9 per rank on several)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -1093,7 +1094,9 @@ def main():
 
     # end to end through the host-buffer entry point (copies inside the timed region)
     # the sample is bounded by the host memory the ranks of this machine can pin together
-    e_bytes = min(float(args.e2e_bytes), 0.35 * host_memory_available() / max(world, 1))
+    # (several ranks pin and copy their samples at once through the same host: 4 GB per rank there)
+    want_bytes = float(args.e2e_bytes) if args.e2e_bytes is not None else (16e9 if world == 1 else 4e9)
+    e_bytes = min(want_bytes, 0.35 * host_memory_available() / max(world, 1))
     arr, keep, e_flops, e_h2d, e_d2h = batch.host_sample(int(e_bytes), 1 << 20)
     n_sample = len(keep[2])
     e_steps = max(3, min(args.steps, 5))
