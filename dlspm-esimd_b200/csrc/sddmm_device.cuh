@@ -2,10 +2,12 @@
 //
 // Lane layout of the fast path (rows of N = 4*chunks floats, 16-byte aligned): the warp is cut
 // into 32/G groups of G lanes.  Lane t of a group owns the float4 chunks r*G + t (r = 0..R-1) of a
-// dense row, so a group reads G*16 contiguous bytes of a row per load (G >= 8: at least one full
-// 128-byte line).  One pass handles 32 nonzeros: group g takes the nonzeros g*G .. g*G+G-1 of the
-// pass and every lane keeps G partial dot products.  A transposing butterfly then leaves, on lane
-// g*G + t, the finished dot product of nonzero g*G + t: G-1 shuffles per lane for G results,
+// dense row, so a group reads G*16 contiguous bytes of a row per load (from G = 8 on at least one
+// full 128-byte line; rows of up to 32 floats use G = 4, see the launchers).  One pass handles 32
+// nonzeros, G per group, and every lane keeps G partial dot products.  In sddmm_pass (used where
+// warps share the nonzeros inside a pass) group g takes the nonzeros g*G .. g*G+G-1; in
+// sddmm_pass_dealt (everywhere else) the nonzeros are dealt to the groups in turn.  A transposing
+// butterfly then leaves one finished dot product on every lane: G-1 shuffles per lane for G results,
 // instead of log2(G) shuffles per result.
 #pragma once
 #include <cuda_runtime.h>
@@ -170,7 +172,8 @@ __device__ __forceinline__ float sddmm_pass_dealt(const float4 (&a)[R], const fl
 
 __device__ __forceinline__ int sddmm_dealt_slot(int G, int g, int t) { return t * (32 / G) + g; }
 
-// Group width and chunks per lane for a row of `chunks` float4: G*R >= chunks with G >= 8.
+// Group width and chunks per lane for a row of `chunks` float4: G*R >= chunks with G >= 8 (the
+// launchers take G = 4 for rows of up to 32 floats by themselves).
 // Returns false when the row is too long for the register-resident path.
 __host__ __device__ inline bool sddmm_layout(int chunks, int *G, int *R)
 {
