@@ -8,7 +8,9 @@
 // counter (thread blocks pull tiles of eight where the fused chain shares rows between warps), one
 // warp per row, and every row is processed exactly as in the
 // single-matrix kernels (same passes, same butterfly, same order of additions), so results have the
-// same bits.  A batch with one inner dimension is one launch; a mixed batch is at most twelve.
+// same bits (one exception: rows of exactly 32 floats in single-matrix launches of 8192 rows or more use
+// 256-bit loads there and can differ in the last place).  A batch with one inner dimension is one
+// launch; a mixed batch is at most twelve.
 #include <algorithm>
 #include <vector>
 
